@@ -1,0 +1,200 @@
+"""ctypes front end of the CPU oracle (``liboracle.so``, built from ``nvfp4_oracle.c`` and
+``adamw_oracle.c`` by ``oracle/Makefile``).
+
+TEST INFRASTRUCTURE ONLY.  The oracle restates the reference's NVFP4 arithmetic on the CPU so that
+the CUDA kernels can be checked bit for bit; it is also the timed CPU baseline of the benchmark.
+Only the test-suite, the smoke test and the benchmark's CPU-baseline leg may import this package.
+The product package never does and fails loudly when its CUDA library is missing.
+
+Arrays are numpy; BF16/FP16 tensors travel as ``uint16`` bit patterns.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB = None
+
+F32, BF16, F16 = 0, 1, 2
+RNE, SR_HASH, SR_PHILOX, SR_MIX = 0, 1, 2, 3
+
+
+def build(force: bool = False) -> Path:
+    """Compile the oracle with the system gcc (a second or two)."""
+    target = _HERE / "liboracle.so"
+    sources = [_HERE / "nvfp4_oracle.c", _HERE / "adamw_oracle.c"]
+    if force or not target.exists() or any(s.stat().st_mtime > target.stat().st_mtime for s in sources):
+        subprocess.run(["make", "-C", str(_HERE), "-B", "liboracle.so"], check=True, capture_output=True)
+    return target
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(str(build()))
+        L = _LIB
+        L.orc_f32_to_bf16.restype = C.c_uint16; L.orc_f32_to_bf16.argtypes = [C.c_float]
+        L.orc_f32_to_f16.restype = C.c_uint16; L.orc_f32_to_f16.argtypes = [C.c_float]
+        L.orc_f16_to_f32.restype = C.c_float; L.orc_f16_to_f32.argtypes = [C.c_uint16]
+        L.orc_f32_to_e4m3.restype = C.c_uint8; L.orc_f32_to_e4m3.argtypes = [C.c_float]
+        L.orc_e4m3_to_f32.restype = C.c_float; L.orc_e4m3_to_f32.argtypes = [C.c_uint8]
+        L.orc_f32_to_e2m1_rne.restype = C.c_uint8; L.orc_f32_to_e2m1_rne.argtypes = [C.c_float]
+        L.orc_e2m1_to_f32.restype = C.c_float; L.orc_e2m1_to_f32.argtypes = [C.c_uint8]
+        L.orc_hash32.restype = C.c_uint32; L.orc_hash32.argtypes = [C.c_uint32, C.c_uint32]
+        L.orc_philox4x32_10.restype = None
+        L.orc_philox4x32_10.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.orc_scale_offset.restype = C.c_int64; L.orc_scale_offset.argtypes = [C.c_int64] * 3
+        L.orc_amax.restype = C.c_float
+        L.orc_amax.argtypes = [C.c_void_p, C.c_int] + [C.c_int64] * 4
+        L.orc_pts.restype = C.c_float; L.orc_pts.argtypes = [C.c_float, C.c_float, C.c_int]
+        L.orc_quantize.restype = None
+        L.orc_quantize.argtypes = ([C.c_void_p, C.c_int] + [C.c_int64] * 6 + [C.c_int, C.c_int, C.c_void_p,
+                                   C.c_uint32, C.c_float, C.c_int, C.c_void_p, C.c_void_p])
+        L.orc_dequantize.restype = None
+        L.orc_dequantize.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
+        L.orc_decode_unscaled.restype = None
+        L.orc_decode_unscaled.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
+        L.orc_rescale.restype = None
+        L.orc_rescale.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_int64, C.c_int64,
+                                  C.c_int64, C.c_int, C.c_void_p]
+    return _LIB
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def round128(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+def dtype_code(a: np.ndarray, kind: str | None = None) -> int:
+    """numpy float32 -> F32; uint16 -> BF16 unless kind == 'f16'."""
+    if a.dtype == np.float32:
+        return F32
+    if a.dtype == np.uint16:
+        return F16 if kind == "f16" else BF16
+    if a.dtype == np.float16:
+        return F16
+    raise TypeError(f"unsupported oracle dtype {a.dtype}")
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bit patterns, round to nearest even (vectorised)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def default_signs(seed: int = 1) -> np.ndarray:
+    """The 16 +-1 floats of nvfp4_fast_v2.get_signs (nvfp4_fast_v2.py:145-150); seed 1 there."""
+    import torch
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randint(0, 2, (16,), generator=gen).float() * 2 - 1).numpy().copy()
+
+
+def amax(x: np.ndarray, m=None, k=None, s0=None, s1=None, kind=None) -> float:
+    """max |bf16(x)| of the logical view; strides are in elements."""
+    base = x if x.dtype != np.float16 else x.view(np.uint16)
+    if m is None:
+        m, k = x.shape
+        s0, s1 = (s // x.itemsize for s in x.strides)
+    return float(lib().orc_amax(_ptr(base), dtype_code(x, kind), m, k, s0, s1))
+
+
+def pts(amax_value: float, factor: float = 1.0, variant: int = 0) -> float:
+    return float(lib().orc_pts(C.c_float(amax_value), C.c_float(factor), variant))
+
+
+def quantize(x: np.ndarray, *, sr_mode=RNE, rht=False, signs=None, seed=0, pts_value=None, transpose=False,
+             hi_first=False, kind=None, variant=0):
+    """Quantise the 2-D array x (or its transpose) to (packed[mp,kp/2], scales[mp/128*32,kp/64*16], pts).
+
+    Mirrors quantize() of nvfp4_fast_v2.py:165-194 over quantize_cuda (csrc/kernels.cu:237-298).
+    """
+    if x.ndim != 2:
+        raise ValueError("oracle quantize expects a 2-D array")
+    base = x if x.dtype != np.float16 else x.view(np.uint16)
+    m, k = x.shape
+    s0, s1 = (s // x.itemsize for s in x.strides)
+    if transpose:
+        m, k, s0, s1 = k, m, s1, s0
+    mp, kp = round128(m), round128(k)
+    code = dtype_code(x, kind)
+    if pts_value is None:
+        a = lib().orc_amax(_ptr(base), code, m, k, s0, s1)
+        pts_value = pts(a, 4.0 if rht else 1.0, variant)
+    if signs is None:
+        signs = default_signs()
+    signs = np.ascontiguousarray(signs, dtype=np.float32)
+    packed = np.empty((mp, kp // 2), dtype=np.uint8)
+    scales = np.empty((mp // 128 * 32, kp // 64 * 16), dtype=np.uint8)
+    lib().orc_quantize(_ptr(base), code, m, k, s0, s1, mp, kp, sr_mode, 16 if rht else 0, _ptr(signs),
+                       C.c_uint32(seed & 0xFFFFFFFF), C.c_float(pts_value), int(hi_first), _ptr(packed), _ptr(scales))
+    return packed, scales, np.float32(pts_value)
+
+
+def dual(x: np.ndarray, *, sr_mode=RNE, signs=None, seed=0, kind=None):
+    """act_pair.dual (act_pair.py:79-102): row packing (no RHT, scale amax/2688, SR seed `seed`) and the
+    transposed packing with the sign*H16/4 transform along the rows of x (scale 4*amax/2688, seed+1)."""
+    a = amax(x, kind=kind)
+    row = quantize(x, sr_mode=sr_mode, rht=False, signs=signs, seed=seed, pts_value=pts(a, 1.0), kind=kind)
+    col = quantize(x, sr_mode=sr_mode, rht=True, signs=signs, seed=seed + 1, pts_value=pts(a, 4.0), transpose=True, kind=kind)
+    return row, col
+
+
+def weight_pair(w: np.ndarray, pts_value=None, kind=None):
+    """quant_weight_pair / pair() (csrc/kernels.cu:165-185, pair.py:25-49): both contraction
+    directions, RNE, no RHT, one shared tensor scale."""
+    if pts_value is None:
+        pts_value = pts(amax(w, kind=kind), 1.0)
+    row = quantize(w, pts_value=pts_value, kind=kind)
+    col = quantize(w, pts_value=pts_value, transpose=True, kind=kind)
+    return row, col
+
+
+def dequantize(packed, scales, pts_value, rows, cols, hi_first=False) -> np.ndarray:
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().orc_dequantize(_ptr(packed), _ptr(scales), C.c_float(pts_value), packed.shape[1] * 2, rows, cols,
+                         int(hi_first), _ptr(out))
+    return out
+
+
+def decode_unscaled(packed, scales, rows=None, cols=None) -> np.ndarray:
+    rows = packed.shape[0] if rows is None else rows
+    cols = packed.shape[1] * 2 if cols is None else cols
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().orc_decode_unscaled(_ptr(packed), _ptr(scales), packed.shape[1] * 2, rows, cols, _ptr(out))
+    return out
+
+
+def rescale(raw: np.ndarray, pts_a, pts_b, rows, cols, *, raw_bf16=True, out_bf16=True, bias=None) -> np.ndarray:
+    raw = np.ascontiguousarray(raw, dtype=np.float32)
+    out = np.empty((rows, cols), dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    lib().orc_rescale(_ptr(raw), int(raw_bf16), C.c_float(pts_a), C.c_float(pts_b), _ptr(b), rows, cols, raw.shape[1],
+                      int(out_bf16), _ptr(out))
+    return out
+
+
+def matmul_packed(a, b, rows, cols, *, raw_bf16=True, out_bf16=True, bias=None) -> np.ndarray:
+    """scale6.matmul (scale6.py:32-39): block-scaled product in FP32, then the rescale chain.
+    a, b are (packed, scales, pts) triples sharing the contraction dimension; result = a @ b.T."""
+    import torch
+    da = torch.from_numpy(decode_unscaled(a[0], a[1]))
+    db = torch.from_numpy(decode_unscaled(b[0], b[1]))
+    raw = (da.double() @ db.double().t()).float().numpy()
+    return rescale(raw, a[2], b[2], rows, cols, raw_bf16=raw_bf16, out_bf16=out_bf16, bias=bias)
+
+
+def philox(ctr, key):
+    c = np.asarray(ctr, dtype=np.uint32); k = np.asarray(key, dtype=np.uint32); o = np.empty(4, dtype=np.uint32)
+    lib().orc_philox4x32_10(_ptr(c), _ptr(k), _ptr(o))
+    return o

@@ -1,0 +1,320 @@
+/*
+ * CPU restatement of the reference NVFP4 quantiser arithmetic.  TEST INFRASTRUCTURE ONLY:
+ * this file is the checker for the CUDA kernels and the timed CPU baseline; no product code
+ * path may call it.
+ *
+ * Every function follows a numbered place in the reference project
+ * (paths relative to the reference repository root):
+ *   input rounding        src/nvfp4_training/_backend/csrc/kernels.cu:19-28
+ *   SR hash + level table src/nvfp4_training/_backend/csrc/kernels.cu:42-58
+ *   tensor scale          src/nvfp4_training/_backend/csrc/kernels.cu:60-78,
+ *                         src/nvfp4_training/_backend/act_pair.py:16-21
+ *   scale swizzle         src/nvfp4_training/_backend/csrc/kernels.cu:80-85
+ *   group math            src/nvfp4_training/_backend/csrc/kernels.cu:87-121
+ *   padding/output shapes src/nvfp4_training/_backend/csrc/kernels.cu:237-298
+ *   dual (row + RHT^T)    src/nvfp4_training/_backend/act_pair.py:50-71
+ *   weight pair           src/nvfp4_training/_backend/pair.py:6-36
+ *   Comfy/H128 variant    src/precision_lora/_packed_cuda.py:14-103,117-163
+ *   E2M1 table / decode   examples/flux2_klein/verify_layout.py:29-40
+ *
+ * Build: gcc -O2 -fopenmp -ffp-contract=off -fno-fast-math -shared -fPIC (see oracle/Makefile).
+ * -ffp-contract=off mirrors the reference's --fmad=false: every * + - / is one IEEE FP32 rounding.
+ *
+ * Parity status: the reference ships no golden byte vectors and none of its code can execute
+ * without an SM120 GPU, so bit patterns are pinned only through the known-answer relations its
+ * tests state (zero stays zero, finish_scale correctly rounded, transpose-requant identity, SR
+ * statistics) and through published known-answer vectors for Philox4x32-10.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+#include <stdlib.h>
+
+#define ORC_F32 0
+#define ORC_BF16 1
+#define ORC_F16 2
+
+#define ORC_RNE 0
+#define ORC_SR_HASH 1
+#define ORC_SR_PHILOX 2
+#define ORC_SR_MIX 3 /* packed backend: mix(i ^ seed), _packed_cuda.py:37,94 */
+
+static inline float bits2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static inline uint32_t f2bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+/* ---- scalar format conversions -------------------------------------------------------- */
+
+uint16_t orc_f32_to_bf16(float f) {
+    uint32_t u = f2bits(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fff;
+    return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+float orc_bf16_to_f32(uint16_t h) { return bits2f((uint32_t)h << 16); }
+
+float orc_f16_to_f32(uint16_t h) {
+    uint32_t s = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 31u, m = h & 1023u;
+    if (e == 0) {
+        float v = (float)m * 5.9604644775390625e-8f; /* 2^-24 */
+        return s ? -v : v;
+    }
+    if (e == 31) return bits2f(s | 0x7f800000u | (m << 13));
+    return bits2f(s | ((e + 112u) << 23) | (m << 13));
+}
+
+uint16_t orc_f32_to_f16(float f) { /* round to nearest even, IEEE binary16 */
+    uint32_t u = f2bits(f), s = (u >> 16) & 0x8000u, a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint16_t)(s | 0x7e00u);
+    if (a >= 0x47800000u) return (uint16_t)(s | 0x7c00u);      /* >= 65536 -> inf (65520 rounds too, below) */
+    if (a < 0x38800000u) {                                     /* below 2^-14: subnormal half */
+        float scaled = bits2f(a) * 16777216.0f;                /* exact: value / 2^-24 */
+        float r = nearbyintf(scaled);
+        return (uint16_t)(s | (uint32_t)r);
+    }
+    uint32_t mant = a & 0x7fffffu, e = (a >> 23) - 112u;
+    uint32_t half = (e << 10) | (mant >> 13), rem = mant & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1u))) half++;
+    return (uint16_t)(s | half);                               /* carries into exponent / inf naturally */
+}
+
+/* E4M3 (fn): bias 7, 3 mantissa bits, max 448, 0x7f is NaN.  RNE with saturation to 448,
+ * i.e. what __nv_fp8_e4m3(float) does for the range the quantiser feeds it (kernels.cu:104-105). */
+uint8_t orc_f32_to_e4m3(float v) {
+    uint8_t s = 0;
+    if (signbit(v)) { s = 0x80; v = -v; }
+    if (!(v == v)) return (uint8_t)(s | 0x7f);
+    if (v >= 464.0f) return (uint8_t)(s | 0x7e);
+    if (v < 0.015625f) {
+        int q = (int)nearbyintf(v * 512.0f);
+        return (uint8_t)(s | q); /* q == 8 is exactly the smallest normal code */
+    }
+    int e; (void)frexpf(v, &e); e -= 1;          /* v in [2^e, 2^(e+1)) */
+    int q = (int)nearbyintf(ldexpf(v, 3 - e));   /* 8..16 */
+    if (q == 16) { e += 1; q = 8; }
+    int code = ((e + 7) << 3) | (q - 8);
+    if (code > 0x7e) code = 0x7e;
+    return (uint8_t)(s | code);
+}
+float orc_e4m3_to_f32(uint8_t x) {
+    int e = (x >> 3) & 15, m = x & 7;
+    float v = e ? ldexpf(1.0f + (float)m * 0.125f, e - 7) : (float)m * 0.001953125f;
+    return (x & 128) ? -v : v;
+}
+
+static const float E2M1_LEVEL[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+float orc_e2m1_to_f32(uint8_t c) { float v = E2M1_LEVEL[c & 7]; return (c & 8) ? -v : v; }
+
+/* cvt.rn.satfinite.e2m1x2.f32 for one value: nearest level, ties to the even code, sign kept. */
+uint8_t orc_f32_to_e2m1_rne(float v) {
+    float a = fabsf(v);
+    int c;
+    if (!(a == a)) c = 7;
+    else if (a <= 0.25f) c = 0;
+    else if (a < 0.75f) c = 1;
+    else if (a <= 1.25f) c = 2;
+    else if (a < 1.75f) c = 3;
+    else if (a <= 2.5f) c = 4;
+    else if (a < 3.5f) c = 5;
+    else if (a <= 5.0f) c = 6;
+    else c = 7;
+    return (uint8_t)(c | (signbit(v) ? 8 : 0));
+}
+
+/* ---- random sources ------------------------------------------------------------------- */
+
+uint32_t orc_hash32(uint32_t seed, uint32_t index) { /* kernels.cu:42-46 before the >>8 */
+    uint32_t z = seed * 0x9e3779b9u + index + 0x85ebca6bu;
+    z ^= z >> 16; z *= 0x7feb352du; z ^= z >> 15; z *= 0x846ca68bu; z ^= z >> 16;
+    return z;
+}
+static inline uint32_t mix32(uint32_t x) { /* _packed_cuda.py:37 */
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16; return x;
+}
+
+/* Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", 2011). */
+void orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+    uint32_t c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+    for (int r = 0; r < 10; ++r) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1;
+        uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1, n3 = (uint32_t)p0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+#define ORC_PHILOX_KEY1 0x4e564634u /* second key word of the SR stream */
+
+/* 24-bit uniform for element `e` (64-bit flat index in the packing's own padded coordinates). */
+static float sr_uniform(int mode, uint32_t seed, uint64_t e) {
+    uint32_t bits;
+    if (mode == ORC_SR_HASH) bits = orc_hash32(seed, (uint32_t)e);
+    else if (mode == ORC_SR_MIX) bits = mix32((uint32_t)e ^ seed);
+    else {
+        uint64_t q = e >> 2;
+        uint32_t ctr[4] = {(uint32_t)q, (uint32_t)(q >> 32), 0u, 0u}, key[2] = {seed, ORC_PHILOX_KEY1}, o[4];
+        orc_philox4x32_10(ctr, key, o);
+        bits = o[e & 3u];
+    }
+    return (float)(bits >> 8) * (1.0f / 16777216.0f);
+}
+
+/* kernels.cu:47-58 — magnitude code by stochastic choice between adjacent levels. */
+static int sr_magnitude(float x, float u) {
+    float lo, hi; int code;
+    if (x < 0.5f) { lo = 0.f; hi = 0.5f; code = 0; }
+    else if (x < 1.f) { lo = 0.5f; hi = 1.f; code = 1; }
+    else if (x < 1.5f) { lo = 1.f; hi = 1.5f; code = 2; }
+    else if (x < 2.f) { lo = 1.5f; hi = 2.f; code = 3; }
+    else if (x < 3.f) { lo = 2.f; hi = 3.f; code = 4; }
+    else if (x < 4.f) { lo = 3.f; hi = 4.f; code = 5; }
+    else if (x < 6.f) { lo = 4.f; hi = 6.f; code = 6; }
+    else return 7;
+    return code + (int)(u < (x - lo) / (hi - lo));
+}
+
+/* ---- layout ---------------------------------------------------------------------------- */
+
+/* kernels.cu:80-85. `col` is an element column. */
+int64_t orc_scale_offset(int64_t row, int64_t col, int64_t padded_k) {
+    return ((row / 128) * (padded_k / 64) + col / 64) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + (col % 64) / 16;
+}
+
+static inline float load_value(const void* x, int dtype, int64_t off) { /* kernels.cu:19-28 */
+    if (dtype == ORC_F32) return orc_bf16_to_f32(orc_f32_to_bf16(((const float*)x)[off]));
+    if (dtype == ORC_BF16) return orc_bf16_to_f32(((const uint16_t*)x)[off]);
+    return orc_bf16_to_f32(orc_f32_to_bf16(orc_f16_to_f32(((const uint16_t*)x)[off])));
+}
+
+/* max |bf16(x)| over the logical m x k view (kernels.cu:60-78). */
+float orc_amax(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1) {
+    float best = 0.f;
+#pragma omp parallel for reduction(max : best) schedule(static)
+    for (int64_t r = 0; r < m; ++r) {
+        float a = 0.f;
+        for (int64_t c = 0; c < k; ++c) a = fmaxf(a, fabsf(load_value(x, dtype, r * s0 + c * s1)));
+        if (a > best) best = a;
+    }
+    return best;
+}
+
+/* Tensor scale variants (they can differ in the last bit; each path uses its own):
+ *  0: (factor*max(a,1e-12)) * (1/(6*448))      kernels.cu:70-77, act_pair.py:19-21, optimizer_v5.py:64
+ *  1: max(a,1e-12) / 2688                      linear6.py:40, frozen.py:59, step6.py:65
+ *  2: max(a/2688, 1e-30)                       _packed_cuda.py:81-83 */
+float orc_pts(float amax, float factor, int variant) {
+    if (variant == 0) return (factor * fmaxf(amax, 1.e-12f)) * (1.f / (6.f * 448.f));
+    if (variant == 1) return fmaxf(amax, 1.e-12f) / 2688.f;
+    return fmaxf(amax / 2688.0f, 1.0e-30f);
+}
+
+/* ---- the group kernel (kernels.cu:87-121) ----------------------------------------------- */
+
+static void hadamard_inplace(float* v, int n, const float* signs, float norm) {
+    for (int l = 0; l < n; ++l) v[l] *= signs[l];
+    float t[128];
+    for (int d = 1; d < n; d *= 2) {
+        for (int l = 0; l < n; ++l) {
+            float other = v[l ^ d];
+            t[l] = (l & d) ? other - v[l] : v[l] + other;
+        }
+        memcpy(v, t, sizeof(float) * (size_t)n);
+    }
+    for (int l = 0; l < n; ++l) v[l] *= norm;
+}
+
+static void encode_group(const float* v, float pts, int sr_mode, uint32_t seed, int64_t row, int64_t col0,
+                         int64_t kp, uint8_t* codes, uint8_t* scale_byte) {
+    float a = 0.f;
+    for (int l = 0; l < 16; ++l) a = fmaxf(a, fabsf(v[l]));
+    float inv = 1.f / pts;
+    float encoded = fminf(fmaxf((a / 6.f) * inv, 0.015625f), 448.f);
+    uint8_t enc8 = orc_f32_to_e4m3(encoded);
+    *scale_byte = enc8;
+    float mul = inv / orc_e4m3_to_f32(enc8);
+    for (int l = 0; l < 16; ++l) {
+        float q = fminf(fmaxf(v[l] * mul, -6.f), 6.f);
+        if (sr_mode == ORC_RNE) codes[l] = orc_f32_to_e2m1_rne(q);
+        else {
+            float u = sr_uniform(sr_mode, seed, (uint64_t)(row * kp + col0 + l));
+            codes[l] = (uint8_t)(sr_magnitude(fabsf(q), u) | ((q < 0.f) ? 8 : 0));
+        }
+    }
+}
+
+/*
+ * Quantise the logical m x k view (element strides s0,s1) into packed[mp][kp/2] and the swizzled
+ * scales[(mp/128*32) x (kp/64*16)], virtually zero-padding to mp x kp.  rht = 0 or 16: the sign *
+ * Hadamard butterfly runs over each 16 consecutive elements of the contraction (last) dimension.
+ * hi_first = 0: byte = even | odd<<4 (kernels.cu:112,117); 1: the Comfy order (_packed_cuda.py:96,99).
+ * A transposed packing is obtained by calling with swapped m/k and strides.
+ */
+void orc_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,
+                  int sr_mode, int rht, const float* signs, uint32_t seed, float pts, int hi_first,
+                  uint8_t* packed, uint8_t* scales) {
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < mp; ++row) {
+        for (int64_t c0 = 0; c0 < kp; c0 += 16) {
+            float v[16]; uint8_t codes[16], sb;
+            for (int l = 0; l < 16; ++l) {
+                int64_t c = c0 + l;
+                v[l] = (row < m && c < k) ? load_value(x, dtype, row * s0 + c * s1) : 0.f;
+            }
+            if (rht) hadamard_inplace(v, 16, signs, 0.25f);
+            encode_group(v, pts, sr_mode, seed, row, c0, kp, codes, &sb);
+            scales[orc_scale_offset(row, c0, kp)] = sb;
+            for (int l = 0; l < 16; l += 2) {
+                uint8_t b = hi_first ? (uint8_t)((codes[l] << 4) | codes[l + 1]) : (uint8_t)(codes[l] | (codes[l + 1] << 4));
+                packed[row * (kp / 2) + (c0 + l) / 2] = b;
+            }
+        }
+    }
+}
+
+/* Decode rows x cols of a packing back to FP32: (level * block_scale) * pts. */
+void orc_dequantize(const uint8_t* packed, const uint8_t* scales, float pts, int64_t kp, int64_t rows, int64_t cols,
+                    int hi_first, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t c = 0; c < cols; ++c) {
+            uint8_t b = packed[r * (kp / 2) + c / 2];
+            uint8_t code = ((c & 1) ^ hi_first) ? (uint8_t)(b >> 4) : (uint8_t)(b & 15);
+            float s = orc_e4m3_to_f32(scales[orc_scale_offset(r, c, kp)]);
+            out[r * cols + c] = (orc_e2m1_to_f32(code) * s) * pts;
+        }
+}
+
+/* Same decode without the tensor scale (what the block-scaled MMA consumes). */
+void orc_decode_unscaled(const uint8_t* packed, const uint8_t* scales, int64_t kp, int64_t rows, int64_t cols,
+                         float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t c = 0; c < cols; ++c) {
+            uint8_t b = packed[r * (kp / 2) + c / 2];
+            uint8_t code = (c & 1) ? (uint8_t)(b >> 4) : (uint8_t)(b & 15);
+            out[r * cols + c] = orc_e2m1_to_f32(code) * orc_e4m3_to_f32(scales[orc_scale_offset(r, c, kp)]);
+        }
+}
+
+/* Post-GEMM rounding chain (kernels.cu:210-234): raw is the accumulator already cast to the
+ * raw dtype by the GEMM (BF16 when raw_bf16 != 0). */
+void orc_rescale(const float* raw, int raw_bf16, float pts_a, float pts_b, const float* bias, int64_t m, int64_t n,
+                 int64_t stride, int out_bf16, float* out) {
+    float alpha = pts_a * pts_b;
+    if (raw_bf16) alpha = orc_bf16_to_f32(orc_f32_to_bf16(alpha));
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < m; ++r)
+        for (int64_t c = 0; c < n; ++c) {
+            float v = raw[r * stride + c];
+            if (raw_bf16) v = orc_bf16_to_f32(orc_f32_to_bf16(v));
+            v = v * alpha;
+            if (raw_bf16) v = orc_bf16_to_f32(orc_f32_to_bf16(v));
+            if (bias) {
+                float b = bias[c];
+                if (raw_bf16) b = orc_bf16_to_f32(orc_f32_to_bf16(b));
+                v = v + b;
+                if (raw_bf16) v = orc_bf16_to_f32(orc_f32_to_bf16(v));
+            }
+            if (out_bf16) v = orc_bf16_to_f32(orc_f32_to_bf16(v));
+            out[r * n + c] = v;
+        }
+}
