@@ -1,0 +1,105 @@
+/*
+ * C ABI of libnvfp4_b200.so — hand-written sm_100a CUDA kernels for the NVFP4 training hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; none allocates, none
+ * synchronises, none keeps global device state, so all of them are safe under CUDA-graph capture
+ * (the quantiser's amax stage uses caller-provided scratch that must start zeroed once and then
+ * resets itself).  Return value: NVFP4_OK or one of the codes below; nvfp4_last_error() gives the
+ * message of the calling thread's last failure.
+ *
+ * Each declaration names the reference interface it replaces (paths inside the reference
+ * project xl03-bit/sm120-nvfp4-training).
+ */
+#ifndef NVFP4_B200_H
+#define NVFP4_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* nvfp4_stream_t; /* a cudaStream_t */
+
+enum {
+    NVFP4_OK = 0,
+    NVFP4_ERR_ARG = 1,         /* null pointer, non-positive size, padded size not a multiple of 128 ... */
+    NVFP4_ERR_ALIGN = 2,       /* pointer or stride alignment the kernel needs is not met */
+    NVFP4_ERR_DTYPE = 3,       /* unknown element type code */
+    NVFP4_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch (message has the CUDA error) */
+    NVFP4_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up (status word written by the kernel) */
+    NVFP4_ERR_UNSUPPORTED = 6  /* valid request this build does not implement */
+};
+
+/* element type codes */
+enum { NVFP4_F32 = 0, NVFP4_BF16 = 1, NVFP4_F16 = 2, NVFP4_E4M3 = 3 };
+
+/* per-orientation flags of the quantiser */
+enum {
+    NVFP4_Q_RHT = 1,        /* sign * H16 / 4 over each 16 contraction elements before scaling */
+    NVFP4_Q_SR_HASH = 2,    /* stochastic rounding, the reference's 32-bit integer hash */
+    NVFP4_Q_SR_PHILOX = 4,  /* stochastic rounding, Philox4x32-10 keyed by the seed */
+    NVFP4_Q_HI_FIRST = 8    /* even element in the high nibble (Comfy checkpoint order) */
+};
+
+const char* nvfp4_last_error(void);
+int nvfp4_version(void);
+
+/* Number of bytes of zero-initialised scratch nvfp4_amax / nvfp4_quantize need (constant). */
+int64_t nvfp4_amax_scratch_bytes(void);
+
+/*
+ * max |bf16(x)| of the logical rows x cols view with element strides (row_stride, col_stride),
+ * and the tensor scales derived from it:
+ *   out[0] = amax
+ *   out[1] = (1 * max(amax,1e-12)) * (1/2688)      row / non-RHT scale
+ *   out[2] = (4 * max(amax,1e-12)) * (1/2688)      RHT scale
+ *   out[3] = max(amax,1e-12) / 2688                true-division variant
+ * Replaces reduce_input + finish_reduce (src/nvfp4_training/_backend/csrc/kernels.cu:60-78, launch at
+ * :255-275) and _absmax + _scale (src/nvfp4_training/_backend/act_pair.py:9-21).
+ */
+int nvfp4_amax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
+               void* scratch, float* out4, nvfp4_stream_t stream);
+
+/*
+ * Tile quantiser: one read of the rows x cols source produces up to two NVFP4 packings.
+ *   "row" packing  = packing of x      : row_packed[rows_p][cols_p/2], row_scales swizzled, groups along cols
+ *   "col" packing  = packing of x^T    : col_packed[cols_p][rows_p/2], col_scales swizzled, groups along rows
+ * rows_p / cols_p are rows / cols rounded up to 128; the padding is written as zeros.  Pass a null
+ * packed pointer to skip an orientation.  *_pts point at the FP32 tensor scale on the device,
+ * *_flags are NVFP4_Q_* bits, *_seed the SR seed; seed_base (nullable, device int32[1]) is added to
+ * both seeds on the device so that CUDA-graph replays draw fresh SR noise.  signs = 16 device floats.
+ * Replaces quant_rows / quant_transpose / quant_weight_pair (csrc/kernels.cu:123-185; device-seed
+ * variant csrc_graph/kernels.cu:126-127), _dual (act_pair.py:50-71), _pair (pair.py:25-36) and _single
+ * (remat.py:7-19).
+ */
+int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
+                        const float* signs, const int32_t* seed_base,
+                        uint8_t* row_packed, uint8_t* row_scales, const float* row_pts, int row_flags, uint32_t row_seed,
+                        uint8_t* col_packed, uint8_t* col_scales, const float* col_pts, int col_flags, uint32_t col_seed,
+                        nvfp4_stream_t stream);
+
+/*
+ * The reference's native operator `quantize` (src/nvfp4_training/_backend/csrc/bindings.cpp:9-12 over
+ * quantize_cuda, csrc/kernels.cu:237-298): quantise the strided m x k view x into packed[mp][kp/2],
+ * scales and pts.  given_scale != null reuses a tensor scale (then pts_out may be null); pair != 0
+ * additionally writes the transposed packing (contiguous FP32/FP16/BF16 weights, RNE, no RHT).
+ * sr: 0 RNE, NVFP4_Q_SR_HASH or NVFP4_Q_SR_PHILOX.  scratch: nvfp4_amax_scratch_bytes() bytes.
+ */
+int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,
+                   int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,
+                   const int32_t* seed_base, int pair, uint8_t* packed, uint8_t* scales, float* pts_out,
+                   uint8_t* packed_t, uint8_t* scales_t, void* scratch, nvfp4_stream_t stream);
+
+/*
+ * NVFP4 -> FP32 or BF16: out[r][c] = (level * block_scale) * pts for r < rows, c < cols.
+ * Replaces dequant (src/precision_lora/_packed_cuda.py:56-63) and the TorchAO NVFP4Tensor.dequantize used
+ * by the reference's verifier (src/nvfp4_training/_verification/nvfp4_cuda.py:184-200).
+ */
+int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* pts, int64_t kp, int64_t rows,
+                     int64_t cols, int hi_first, int out_dtype, void* out, int64_t out_stride, nvfp4_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,146 @@
+"""ctypes binding of libnvfp4_b200.so (the C ABI declared in include/nvfp4_b200.h).
+
+PyTorch supplies device memory and streams only; every kernel on the NVFP4 path lives in the shared
+library.  There is no CPU or eager fallback: a missing library raises at first use.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libnvfp4_b200.so"
+_HEADER = Path(__file__).resolve().parents[2] / "include" / "nvfp4_b200.h"
+_lib = None
+
+F32, BF16, F16, E4M3 = 0, 1, 2, 3
+Q_RHT, Q_SR_HASH, Q_SR_PHILOX, Q_HI_FIRST = 1, 2, 4, 8
+_CODES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+_ERRORS = {1: ValueError, 2: ValueError, 3: TypeError, 4: RuntimeError, 5: RuntimeError, 6: NotImplementedError}
+
+P, I64, I32, U32, F = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_float
+
+_SIGNATURES = {
+    "nvfp4_last_error": (C.c_char_p, []),
+    "nvfp4_version": (I32, []),
+    "nvfp4_amax_scratch_bytes": (I64, []),
+    "nvfp4_amax": (I32, [P, I32, I64, I64, I64, I64, P, P, P]),
+    "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P]),
+    "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P]),
+    "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
+}
+
+
+def declared_symbols() -> list[str]:
+    """Names of the entry points the public header declares."""
+    text = _HEADER.read_text()
+    return sorted(set(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib():
+    """Load the CUDA library once; never falls back to another implementation."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(f"{_LIB_PATH} is missing: build it with `python sm120-nvfp4-training_b200/build.py` "
+                               "(no CPU or eager fallback exists for the NVFP4 path)")
+        handle = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(code: int) -> None:
+    if code:
+        message = lib().nvfp4_last_error().decode("utf-8", "replace")
+        raise _ERRORS.get(code, RuntimeError)(message)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise TypeError(f"Unsupported dtype {t.dtype}; use BF16 autocast / FP32 or FP16 masters") from None
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+_SCRATCH: dict[tuple, torch.Tensor] = {}
+
+
+def scratch(device: torch.device) -> torch.Tensor:
+    """Zero-initialised amax scratch, one per (device, stream): the kernels leave it zeroed again."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _SCRATCH.get(key)
+    if buf is None:
+        buf = torch.zeros(int(lib().nvfp4_amax_scratch_bytes()), dtype=torch.uint8, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def round128(n: int) -> int:
+    if n <= 0:
+        raise ValueError("Empty dimensions are not supported")
+    return (n + 127) // 128 * 128
+
+
+def amax(x: torch.Tensor) -> torch.Tensor:
+    """float32[4] on the device: amax, scale, 4x scale, true-division scale (see nvfp4_amax)."""
+    out = torch.empty(4, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().nvfp4_amax(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1),
+                               scratch(x.device).data_ptr(), out.data_ptr(), stream_of(x)))
+    return out
+
+
+def quantize_tile(x, signs, *, row=None, col=None, seed_base=None):
+    """row / col: None or dict(packed, scales, pts, flags, seed)."""
+    def unpack(o):
+        if o is None:
+            return None, None, None, 0, 0
+        return o["packed"].data_ptr(), o["scales"].data_ptr(), o["pts"].data_ptr(), int(o.get("flags", 0)), int(o.get("seed", 0)) & 0xFFFFFFFF
+    rp, rs, rq, rf, rsd = unpack(row)
+    cp, cs, cq, cf, csd = unpack(col)
+    with torch.cuda.device(x.device):
+        check(lib().nvfp4_quantize_tile(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1),
+                                        signs.data_ptr(), ptr(seed_base), rp, rs, rq, rf, rsd, cp, cs, cq, cf, csd,
+                                        stream_of(x)))
+
+
+def quantize(x, signs, mp, kp, sr, rht, seed, given_scale=None, pair=False, seed_base=None):
+    """The reference's native `quantize` operator: returns [packed, scales, pts(, packed_t, scales_t)]."""
+    if x.dim() != 2 or not x.is_cuda:
+        raise RuntimeError("quantize requires a CUDA 2D tensor")
+    dev = x.device
+    packed = torch.empty((mp, kp // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((mp // 128 * 32, kp // 64 * 16), dtype=torch.uint8, device=dev)
+    pts = given_scale if given_scale is not None else torch.empty((), dtype=torch.float32, device=dev)
+    dt = st = None
+    if pair:
+        dt = torch.empty((kp, mp // 2), dtype=torch.uint8, device=dev)
+        st = torch.empty((kp // 128 * 32, mp // 64 * 16), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().nvfp4_quantize(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1), mp, kp,
+                                   int(sr), int(bool(rht)), int(seed) & 0xFFFFFFFF, signs.data_ptr(), ptr(given_scale),
+                                   ptr(seed_base), int(bool(pair)), packed.data_ptr(), scales.data_ptr(),
+                                   None if given_scale is not None else pts.data_ptr(), ptr(dt), ptr(st),
+                                   scratch(dev).data_ptr(), stream_of(x)))
+    return [packed, scales, pts, dt, st] if pair else [packed, scales, pts]
+
+
+def dequantize(packed, scales, pts, rows, cols, *, hi_first=False, dtype=torch.float32):
+    out = torch.empty((rows, cols), dtype=dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().nvfp4_dequantize(packed.data_ptr(), scales.data_ptr(), pts.data_ptr(), packed.shape[1] * 2, rows, cols,
+                                     int(hi_first), dtype_code(out), out.data_ptr(), out.stride(0), stream_of(packed)))
+    return out
