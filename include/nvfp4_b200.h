@@ -99,6 +99,24 @@ int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, i
 int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* pts, int64_t kp, int64_t rows,
                      int64_t cols, int hi_first, int out_dtype, void* out, int64_t out_stride, nvfp4_stream_t stream);
 
+/*
+ * Block-scaled NVFP4 GEMM with fused epilogue:  out[rows x cols] = crop((A o SFA) (B o SFB)^T) * alpha (+ bias).
+ *   a [M][K/2], b [N][K/2]: e2m1 payloads (low nibble = even element), K-major; sfa, sfb: swizzled ue4m3 block
+ *   scales as the quantiser writes them; M, N, K multiples of 128; FP32 accumulation (tcgen05, TMEM).
+ *   pts_a, pts_b: device FP32 tensor scales, alpha = pts_a * pts_b; both null = store the raw accumulator.
+ *   raw_bf16 != 0 reproduces the reference's BF16 chain: bf16(acc), alpha -> bf16, bf16(raw * alpha),
+ *   bf16(y + bf16(bias)); raw_bf16 == 0 is the FP32 chain acc * alpha (+ bias).
+ *   out: FP32 or BF16, row stride ldo elements.  status: nullable device int, set to NVFP4_ERR_TIMEOUT if a
+ *   bounded device-side wait expired (the kernel then returns early instead of hanging).
+ * Replaces torch._scaled_mm on float4_e2m1fn_x2 operands (src/nvfp4_training/_backend/nvfp4_fast_v2.py:208-215,
+ * scale6.py:35-37, nvfp4_v5.py:122-125, linear6.py:141-144; src/precision_lora/_packed_cuda.py:244-249) together
+ * with the separate `rescale` operator (csrc/bindings.cpp:9-12 over rescale_cuda, csrc/kernels.cu:210-234,300-328;
+ * scale6.py:7-30).
+ */
+int nvfp4_gemm(const uint8_t* a, const uint8_t* sfa, const float* pts_a, const uint8_t* b, const uint8_t* sfb,
+               const float* pts_b, int64_t M, int64_t N, int64_t K, const void* bias, int bias_dtype, void* out,
+               int out_dtype, int64_t ldo, int64_t rows, int64_t cols, int raw_bf16, int* status, nvfp4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

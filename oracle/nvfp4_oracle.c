@@ -144,16 +144,18 @@ void orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t ou
 }
 #define ORC_PHILOX_KEY1 0x4e564634u /* second key word of the SR stream */
 
-/* 24-bit uniform for element `e` (64-bit flat index in the packing's own padded coordinates). */
+/* Uniform in [0,1) for element `e` (64-bit flat index in the packing's own padded coordinates).
+ * Hash sources: 24 bits.  Philox: one 128-bit block per 8 consecutive elements, 16 bits each
+ * (counter = e >> 3, word (e >> 1) & 3, low half for even e), key = (seed, ORC_PHILOX_KEY1). */
 static float sr_uniform(int mode, uint32_t seed, uint64_t e) {
     uint32_t bits;
     if (mode == ORC_SR_HASH) bits = orc_hash32(seed, (uint32_t)e);
     else if (mode == ORC_SR_MIX) bits = mix32((uint32_t)e ^ seed);
     else {
-        uint64_t q = e >> 2;
+        uint64_t q = e >> 3;
         uint32_t ctr[4] = {(uint32_t)q, (uint32_t)(q >> 32), 0u, 0u}, key[2] = {seed, ORC_PHILOX_KEY1}, o[4];
         orc_philox4x32_10(ctr, key, o);
-        bits = o[e & 3u];
+        return (float)((o[(e >> 1) & 3u] >> ((e & 1u) * 16)) & 0xffffu) * (1.0f / 65536.0f);
     }
     return (float)(bits >> 8) * (1.0f / 16777216.0f);
 }

@@ -71,15 +71,17 @@ __device__ __forceinline__ float uniform24(uint32_t bits) {
 }
 
 // ---- E2M1 stochastic level choice ---------------------------------------------------------------
-__device__ __forceinline__ int sr_magnitude(float x, float u) {
-    // lower level, its code and the reciprocal width of the interval that holds x (0 <= x <= 6)
-    float lo, rw; int code;
-    if (x < 2.f) { float t = floorf(x * 2.f); lo = t * .5f; code = static_cast<int>(t); rw = 2.f; }
-    else if (x < 4.f) { lo = floorf(x); code = static_cast<int>(lo) + 2; rw = 1.f; }
-    else if (x < 6.f) { lo = 4.f; code = 6; rw = .5f; }
-    else return 7;
-    // (x - lo) / (hi - lo): the width is a power of two, so the product is the same correctly rounded value
-    return code + static_cast<int>(u < __fmul_rn(__fsub_rn(x, lo), rw));
+__device__ __forceinline__ uint32_t sr_magnitude(float x, float u) {
+    // x in [0, 6].  Level spacing is 1/2 below 2, 1 below 4, 2 above; t counts whole steps from zero of
+    // that spacing, lo = t * spacing is the level at or below x.  (x - lo) / spacing is written as a product:
+    // the spacing is a power of two, so both forms round to the same float.  x == 6 gives lo = 4, p = 1 > u.
+    const bool s2 = x < 2.f, s4 = x < 4.f;
+    const float rw = s2 ? 2.f : (s4 ? 1.f : .5f);
+    const float w = s2 ? .5f : (s4 ? 1.f : 2.f);
+    const float t = s4 ? floorf(__fmul_rn(x, rw)) : 2.f;
+    const float lo = __fmul_rn(t, w);
+    const uint32_t code = static_cast<uint32_t>(t) + (s2 ? 0u : (s4 ? 2u : 4u));
+    return code + static_cast<uint32_t>(u < __fmul_rn(__fsub_rn(x, lo), rw));
 }
 
 // ---- scale-factor swizzle (32 x 4 x 4 atom inside 128-row x 4-group blocks) ------------------------

@@ -1,0 +1,419 @@
+// Block-scaled NVFP4 GEMM for sm_100a:  D[M,N] = (A o SFA) * (B o SFB)^T, FP32 accumulation in TMEM,
+// fused epilogue  y = cast(raw * alpha) (+ bias)  with crop.
+//
+//   A: e2m1 payload [M][K/2] (K-major), SFA: ue4m3, one per 16 elements, in 128-row x 4-scale blocks of
+//      512 bytes ordered [M/128][K/64]; B, SFB likewise with N rows.  M, N, K are multiples of 128.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0   : TMA producer.  Per k-tile of 256 elements: A box 128 rows x 128 B, B box BN rows x 128 B
+//              (both 128-byte swizzled) and the scale blocks as plain bulk copies, all completing on one
+//              mbarrier per stage.  Plain loads only: every CTA fetches its own tiles.
+//   warp 1   : allocates TMEM; one lane issues tcgen05.cp (scale blocks smem -> TMEM) and
+//              tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N x K64) and commits to the stage's
+//              "empty" barrier / the accumulator's "full" barrier.
+//   warps 2-5: epilogue; each owns the 32 TMEM lanes of its sub-partition: tcgen05.ld -> scale -> cast ->
+//              global stores, then releases the accumulator.
+// Every wait is bounded: on expiry the kernel raises the status word, all roles leave their loops, the
+// producer waits (bounded) for loads still in flight, TMEM is freed and the kernel returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
+
+namespace nvfp4 {
+
+constexpr int GEMM_THREADS = 192;
+constexpr int BM = 128;
+constexpr int BK = 256;             // elements per k-tile = 128 payload bytes per row
+constexpr int A_STAGE_BYTES = BM * 128;
+constexpr int SF_BLOCK = 512;       // 128 rows x 4 scales
+constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+template <int BN> struct GemmCfg {
+    static constexpr int B_STAGE_BYTES = BN * 128;
+    static constexpr int SFA_STAGE_BYTES = 4 * SF_BLOCK;
+    static constexpr int SFB_STAGE_BYTES = (BN / 128) * 4 * SF_BLOCK;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;
+    static constexpr int SFA_COLS = 16;             // 4 k-blocks x 4 columns
+    static constexpr int SFB_COLS = 4 * (BN / 32);  // 4 k-blocks x BN/32 columns
+    static constexpr int ACC_COLS = ACC_STAGES * BN;
+    static constexpr int SF_BASE = ACC_COLS;        // two scale buffers (even / odd k-tile) behind the accumulators
+    static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(ACC_COLS + 2 * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
+};
+
+struct GemmArgs {
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    const float* pts_a;  // null: no tensor scaling (raw accumulator output)
+    const float* pts_b;
+    const void* bias;    // null or N-vector
+    void* out;
+    int* status;         // null or device int, set non-zero when a bounded wait expired
+    int64_t ldo;
+    int bias_f32, out_f32, raw_bf16;
+    int M, N, K, rows, cols;
+    int tiles_m, tiles_n, k_tiles;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the time limit passed or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; return false; }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                       uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzled operand tile (rows of 128 bytes, 8-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+    return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// One 512-byte scale block seen as 32 rows x 16 bytes, unswizzled (8-row groups 128 bytes apart).
+__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
+    return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (8ull << 32) | (1ull << 46);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + Cfg::STAGES;
+    uint64_t* acc_full = bars + 2 * Cfg::STAGES;
+    uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + Cfg::ACC_STAGES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < Cfg::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = g.tiles_m * g.tiles_n;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int tm = t % g.tiles_m, tn = t / g.tiles_m;
+                for (int kt = 0; kt < g.k_tiles; ++kt) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = smem + stage * Cfg::STAGE_BYTES;
+                    const int kblocks = min(4, g.K / 64 - kt * 4);
+                    const uint32_t sf_bytes = kblocks * SF_BLOCK;
+                    mbar_expect_tx(&full[stage], A_STAGE_BYTES + Cfg::B_STAGE_BYTES + sf_bytes * (1 + BN / 128));
+                    tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[stage]);
+                    tma_load_2d(st + A_STAGE_BYTES, &map_b, kt * 128, tn * BN, &full[stage]);
+                    const int64_t kb_total = g.K / 64;
+                    bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES, g.sfa + (static_cast<int64_t>(tm) * kb_total + kt * 4) * SF_BLOCK,
+                              sf_bytes, &full[stage]);
+#pragma unroll
+                    for (int nb = 0; nb < BN / 128; ++nb)
+                        bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES + Cfg::SFA_STAGE_BYTES + nb * 4 * SF_BLOCK,
+                                  g.sfb + (static_cast<int64_t>(tn * (BN / 128) + nb) * kb_total + kt * 4) * SF_BLOCK, sf_bytes,
+                                  &full[stage]);
+                    ++issued;
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // loads already issued still write into this CTA's shared memory: give them a bounded chance to land
+                const int pending = min(issued, Cfg::STAGES);
+                int s = stage; uint32_t ph = phase;
+                for (int i = 0; i < pending; ++i) {
+                    if (--s < 0) { s = Cfg::STAGES - 1; ph ^= 1; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(&full[s], ph) && clock64() - t0 < WAIT_CYCLES / 8) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            uint32_t ktile_count = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+                const int acc = local % Cfg::ACC_STAGES;
+                const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + acc * BN;
+                for (int kt = 0; kt < g.k_tiles; ++kt, ++ktile_count) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const uint32_t ssfa = sb + Cfg::B_STAGE_BYTES;
+                    const uint32_t ssfb = ssfa + Cfg::SFA_STAGE_BYTES;
+                    const uint32_t sf_tmem = tmem_base + Cfg::SF_BASE + (ktile_count & 1) * Cfg::SF_BUF_COLS;
+                    const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + Cfg::SFA_COLS;
+                    const int kblocks = min(4, g.K / 64 - kt * 4);
+                    for (int kb = 0; kb < kblocks; ++kb) {
+                        tc_cp_sf(sfa_tmem + kb * 4, scale_desc(ssfa + kb * SF_BLOCK));
+#pragma unroll
+                        for (int nb = 0; nb < BN / 128; ++nb)
+                            tc_cp_sf(sfb_tmem + kb * (BN / 32) + nb * 4, scale_desc(ssfb + (nb * 4 + kb) * SF_BLOCK));
+                    }
+                    for (int kb = 0; kb < kblocks; ++kb) {
+                        tc_mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc,
+                               (kt > 0 || kb > 0) ? 1u : 0u, sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
+                    }
+                    tc_commit(&empty[stage]);
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+        const int row_in_tile = sub * 32 + lane;
+        float alpha = 1.f;
+        const bool scaled = g.pts_a != nullptr;
+        if (scaled) {
+            alpha = __fmul_rn(__ldg(g.pts_a), __ldg(g.pts_b));
+            if (g.raw_bf16) alpha = bf16_value(bf16_bits(alpha));
+        }
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            const int tm = t % g.tiles_m, tn = t / g.tiles_m;
+            const int acc = local % Cfg::ACC_STAGES;
+            const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
+            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int64_t row = static_cast<int64_t>(tm) * BM + row_in_tile;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(taddr + c0, r);
+                tc_wait_ld();
+                const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
+                if (row < g.rows && col0 < g.cols) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(r[j]);
+                        if (g.raw_bf16) x = bf16_value(bf16_bits(x));
+                        if (scaled) {
+                            x = __fmul_rn(x, alpha);
+                            if (g.raw_bf16) x = bf16_value(bf16_bits(x));
+                        }
+                        v[j] = x;
+                    }
+                    if (g.bias) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < g.cols) {
+                                float b = g.bias_f32 ? __ldg(static_cast<const float*>(g.bias) + col0 + j)
+                                                     : bf16_value(__ldg(static_cast<const uint16_t*>(g.bias) + col0 + j));
+                                if (g.raw_bf16) b = bf16_value(bf16_bits(b));
+                                float y = __fadd_rn(v[j], b);
+                                if (g.raw_bf16) y = bf16_value(bf16_bits(y));
+                                v[j] = y;
+                            }
+                        }
+                    }
+                    const bool full_chunk = col0 + 32 <= g.cols;
+                    if (g.out_f32) {
+                        float* dst = static_cast<float*>(g.out) + row * g.ldo + col0;
+                        if (full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (col0 + j < g.cols) dst[j] = v[j];
+                        }
+                    } else {
+                        uint16_t* dst = static_cast<uint16_t*>(g.out) + row * g.ldo + col0;
+                        if (full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 u;
+                                u.x = bf16_bits(v[8 * j]) | (uint32_t(bf16_bits(v[8 * j + 1])) << 16);
+                                u.y = bf16_bits(v[8 * j + 2]) | (uint32_t(bf16_bits(v[8 * j + 3])) << 16);
+                                u.z = bf16_bits(v[8 * j + 4]) | (uint32_t(bf16_bits(v[8 * j + 5])) << 16);
+                                u.w = bf16_bits(v[8 * j + 6]) | (uint32_t(bf16_bits(v[8 * j + 7])) << 16);
+                                reinterpret_cast<uint4*>(dst)[j] = u;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (col0 + j < g.cols) dst[j] = bf16_bits(v[j]);
+                        }
+                    }
+                }
+            }
+            // all of this warp's TMEM reads have completed (wait::ld above): hand the accumulator back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && g.status) atomicExch(g.status, NVFP4_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+    cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& g, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_gemm: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    static int sm_count[64] = {};
+    if (dev < 64 && !sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    const int sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
+    g.tiles_n = g.N / BN;
+    const int grid = std::min(g.tiles_m * g.tiles_n, sms);
+    gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, g);
+    return launch_status("nvfp4_gemm");
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+extern "C" int nvfp4_gemm(const uint8_t* a, const uint8_t* sfa, const float* pts_a, const uint8_t* b, const uint8_t* sfb,
+                          const float* pts_b, int64_t M, int64_t N, int64_t K, const void* bias, int bias_dtype, void* out,
+                          int out_dtype, int64_t ldo, int64_t rows, int64_t cols, int raw_bf16, int* status,
+                          nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(a && sfa && b && sfb && out, NVFP4_ERR_ARG, "nvfp4_gemm: null pointer");
+    NVFP4_REQUIRE((pts_a == nullptr) == (pts_b == nullptr), NVFP4_ERR_ARG, "nvfp4_gemm: give both tensor scales or neither");
+    NVFP4_REQUIRE(M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 128 == 0, NVFP4_ERR_ARG,
+                  "nvfp4_gemm: M, N, K must be positive multiples of 128 (got %lld %lld %lld)", (long long)M, (long long)N, (long long)K);
+    NVFP4_REQUIRE(rows > 0 && cols > 0 && rows <= M && cols <= N && ldo >= cols, NVFP4_ERR_ARG, "nvfp4_gemm: invalid output crop");
+    NVFP4_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), NVFP4_ERR_ARG, "nvfp4_gemm: dimension exceeds 2^31");
+    NVFP4_REQUIRE(out_dtype == NVFP4_F32 || out_dtype == NVFP4_BF16, NVFP4_ERR_DTYPE, "nvfp4_gemm: output must be FP32 or BF16");
+    NVFP4_REQUIRE(!bias || bias_dtype == NVFP4_F32 || bias_dtype == NVFP4_BF16, NVFP4_ERR_DTYPE, "nvfp4_gemm: bias must be FP32 or BF16");
+    for (const void* p : {static_cast<const void*>(a), static_cast<const void*>(b), static_cast<const void*>(sfa), static_cast<const void*>(sfb)})
+        NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_gemm: operands and scales must be 16-byte aligned");
+    GemmArgs g{};
+    g.sfa = sfa; g.sfb = sfb; g.pts_a = pts_a; g.pts_b = pts_b; g.bias = bias; g.out = out; g.status = status;
+    g.ldo = ldo; g.bias_f32 = bias_dtype == NVFP4_F32; g.out_f32 = out_dtype == NVFP4_F32; g.raw_bf16 = raw_bf16 != 0;
+    g.M = static_cast<int>(M); g.N = static_cast<int>(N); g.K = static_cast<int>(K);
+    g.rows = static_cast<int>(rows); g.cols = static_cast<int>(cols);
+    g.tiles_m = g.M / BM; g.k_tiles = (g.K + BK - 1) / BK;
+    const int bn = (N % 256 == 0) ? 256 : 128;
+    CUtensorMap ma, mb;
+    NVFP4_REQUIRE(make_operand_map(&ma, a, M, K, BM) && make_operand_map(&mb, b, N, K, bn), NVFP4_ERR_LAUNCH,
+                  "nvfp4_gemm: cuTensorMapEncodeTiled failed or is unavailable");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    return bn == 256 ? launch_gemm<256>(ma, mb, g, st) : launch_gemm<128>(ma, mb, g, st);
+}

@@ -137,84 +137,89 @@ __global__ void __launch_bounds__(AMAX_THREADS) amax_kernel(const void* __restri
 // ================================================================================================
 // group encoder
 // ================================================================================================
-__device__ __forceinline__ void hadamard16(float (&v)[16], const float (&sg)[16]) {
+// sign * H16 butterfly WITHOUT the final 1/4: that power-of-two factor is folded into the block
+// amax and the element multiplier by the caller, which gives the same bits as scaling the 16 values
+// first (a multiplication by 0.25 is exact).  The first stage absorbs the signs: a product with +-1
+// is exact, so fma(b, s_b, a * s_a) rounds once, exactly like (a * s_a) + (b * s_b).
+__device__ __forceinline__ void hadamard16_unscaled(float (&v)[16], const float (&sg)[16]) {
 #pragma unroll
-    for (int l = 0; l < 16; ++l) v[l] = __fmul_rn(v[l], sg[l]);
+    for (int p = 0; p < 8; ++p) {
+        const float a = __fmul_rn(v[2 * p], sg[2 * p]);
+        const float b = v[2 * p + 1], sb = sg[2 * p + 1];
+        v[2 * p] = __fmaf_rn(b, sb, a);
+        v[2 * p + 1] = __fmaf_rn(b, -sb, a);
+    }
 #pragma unroll
-    for (int d = 1; d < 16; d <<= 1) {
+    for (int d = 2; d < 16; d <<= 1) {
         float t[16];
 #pragma unroll
         for (int l = 0; l < 16; ++l) t[l] = (l & d) ? __fsub_rn(v[l ^ d], v[l]) : __fadd_rn(v[l], v[l ^ d]);
 #pragma unroll
         for (int l = 0; l < 16; ++l) v[l] = t[l];
     }
-#pragma unroll
-    for (int l = 0; l < 16; ++l) v[l] = __fmul_rn(v[l], 0.25f);
 }
 
-// Encodes 16 values.  idx0 = flat index of element 0 in the packing's padded coordinates.
-__device__ __forceinline__ uint2 encode16(const float (&v)[16], float inv_pts, int flags, uint32_t seed, uint64_t idx0,
-                                          uint32_t& scale_byte) {
+constexpr int SR_NONE = 0, SR_HASH = 1, SR_PHILOX = 2;
+__host__ __device__ constexpr int sr_of_flags(int flags) {
+    return (flags & NVFP4_Q_SR_HASH) ? SR_HASH : (flags & NVFP4_Q_SR_PHILOX) ? SR_PHILOX : SR_NONE;
+}
+
+// Encodes 16 values (times `fold` = 0.25 when they come from hadamard16_unscaled, else 1).
+// idx0 = flat index of element 0 in the packing's padded coordinates (a multiple of 16).
+template <int SR>
+__device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float inv_pts, bool hi_first, uint32_t seed,
+                                          uint64_t idx0, uint32_t& scale_byte) {
     float a = 0.f;
 #pragma unroll
     for (int l = 0; l < 16; ++l) a = fmaxf(a, fabsf(v[l]));
-    float enc = fminf(fmaxf(__fmul_rn(__fdiv_rn(a, 6.f), inv_pts), 0.015625f), 448.f);
-    uint32_t e8 = __nv_cvt_float_to_fp8(enc, __NV_SATFINITE, __NV_E4M3);
+    if (fold) a = __fmul_rn(a, 0.25f);
+    const float enc = fminf(fmaxf(__fmul_rn(__fdiv_rn(a, 6.f), inv_pts), 0.015625f), 448.f);
+    const uint32_t e8 = __nv_cvt_float_to_fp8(enc, __NV_SATFINITE, __NV_E4M3);
     scale_byte = e8;
-    const float mul = __fdiv_rn(inv_pts, e4m3_normal_to_float(e8));
-    float q[16];
+    float mul = __fdiv_rn(inv_pts, e4m3_normal_to_float(e8));
+    if (fold) mul = __fmul_rn(mul, 0.25f);
+    uint32_t lo = 0, hi = 0;
+    if constexpr (SR == SR_NONE) {
+        // cvt.rn.satfinite clamps to +-6 by itself
 #pragma unroll
-    for (int l = 0; l < 16; ++l) q[l] = fminf(fmaxf(__fmul_rn(v[l], mul), -6.f), 6.f);
-    uint32_t codes[16];
-    if (flags & (NVFP4_Q_SR_HASH | NVFP4_Q_SR_PHILOX)) {
-        if (flags & NVFP4_Q_SR_HASH) {
-            const uint32_t i0 = static_cast<uint32_t>(idx0);
+        for (int b = 0; b < 4; ++b) {
+            const float q0 = __fmul_rn(v[2 * b], mul), q1 = __fmul_rn(v[2 * b + 1], mul);
+            const float q2 = __fmul_rn(v[8 + 2 * b], mul), q3 = __fmul_rn(v[8 + 2 * b + 1], mul);
+            const float2 p0 = hi_first ? make_float2(q1, q0) : make_float2(q0, q1);
+            const float2 p1 = hi_first ? make_float2(q3, q2) : make_float2(q2, q3);
+            lo |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p0, __NV_E2M1, cudaRoundNearest)) << (8 * b);
+            hi |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p1, __NV_E2M1, cudaRoundNearest)) << (8 * b);
+        }
+        return make_uint2(lo, hi);
+    } else {
+        uint32_t codes[16];
+        uint32_t rnd[8];
+        if constexpr (SR == SR_PHILOX) {
+            const uint64_t c0 = idx0 >> 3;  // one Philox block serves 8 consecutive elements (16 bits each)
 #pragma unroll
-            for (int l = 0; l < 16; ++l) {
-                float u = uniform24(hash32(seed, i0 + l));
-                codes[l] = sr_magnitude(fabsf(q[l]), u) | ((q[l] < 0.f) ? 8u : 0u);
-            }
-        } else {
-            const uint64_t q0 = idx0 >> 2;  // idx0 is a multiple of 16
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint64_t qi = q0 + j;
-                uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(qi), static_cast<uint32_t>(qi >> 32), 0u, 0u),
-                                        seed, PHILOX_KEY1);
-                uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    int l = j * 4 + t;
-                    codes[l] = sr_magnitude(fabsf(q[l]), uniform24(w[t])) | ((q[l] < 0.f) ? 8u : 0u);
-                }
+            for (int j = 0; j < 2; ++j) {
+                const uint64_t ci = c0 + j;
+                const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(ci), static_cast<uint32_t>(ci >> 32), 0u, 0u),
+                                              seed, PHILOX_KEY1);
+                rnd[4 * j] = r.x; rnd[4 * j + 1] = r.y; rnd[4 * j + 2] = r.z; rnd[4 * j + 3] = r.w;
             }
         }
-        uint32_t lo = 0, hi = 0;
-        if (flags & NVFP4_Q_HI_FIRST) {
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                lo |= ((codes[2 * b] << 4) | codes[2 * b + 1]) << (8 * b);
-                hi |= ((codes[8 + 2 * b] << 4) | codes[8 + 2 * b + 1]) << (8 * b);
-            }
-        } else {
+        for (int l = 0; l < 16; ++l) {
+            const float q = __fmul_rn(v[l], mul);
+            float u;
+            if constexpr (SR == SR_HASH) u = uniform24(hash32(seed, static_cast<uint32_t>(idx0) + l));
+            else u = static_cast<float>((rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) * (1.0f / 65536.0f);
+            codes[l] = sr_magnitude(fminf(fabsf(q), 6.f), u) | ((q < 0.f) ? 8u : 0u);
+        }
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                lo |= (codes[2 * b] | (codes[2 * b + 1] << 4)) << (8 * b);
-                hi |= (codes[8 + 2 * b] | (codes[8 + 2 * b + 1] << 4)) << (8 * b);
-            }
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t e0 = codes[2 * b], o0 = codes[2 * b + 1], e1 = codes[8 + 2 * b], o1 = codes[8 + 2 * b + 1];
+            lo |= (hi_first ? ((e0 << 4) | o0) : (e0 | (o0 << 4))) << (8 * b);
+            hi |= (hi_first ? ((e1 << 4) | o1) : (e1 | (o1 << 4))) << (8 * b);
         }
         return make_uint2(lo, hi);
     }
-    uint32_t lo = 0, hi = 0;
-    const bool hf = flags & NVFP4_Q_HI_FIRST;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        float2 p0 = hf ? make_float2(q[2 * b + 1], q[2 * b]) : make_float2(q[2 * b], q[2 * b + 1]);
-        float2 p1 = hf ? make_float2(q[8 + 2 * b + 1], q[8 + 2 * b]) : make_float2(q[8 + 2 * b], q[8 + 2 * b + 1]);
-        lo |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p0, __NV_E2M1, cudaRoundNearest)) << (8 * b);
-        hi |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p1, __NV_E2M1, cudaRoundNearest)) << (8 * b);
-    }
-    return make_uint2(lo, hi);
 }
 
 // ================================================================================================
@@ -273,7 +278,7 @@ __device__ __forceinline__ void load_group_bf16(const void* x, int64_t r, int64_
     for (int l = 0; l < 16; ++l) h[l] = (c0 + l < cols) ? load_as_bf16<DT>(x, r * rs + (c0 + l) * cs) : uint16_t(0);
 }
 
-template <int DT, bool ROW, bool COL>
+template <int DT, bool ROW, bool COL, int SR>
 __global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict__ x, int64_t rows, int64_t cols,
                                                          int64_t rs, int64_t cs, int vec_ok,
                                                          const float* __restrict__ signs,
@@ -315,9 +320,11 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict_
             float v[16];
 #pragma unroll
             for (int l = 0; l < 16; ++l) v[l] = bf16_value(h[l]);
-            if (R.flags & NVFP4_Q_RHT) hadamard16(v, sg);
+            const bool rht = R.flags & NVFP4_Q_RHT;
+            if (rht) hadamard16_unscaled(v, sg);
             uint32_t sb;
-            uint2 p = encode16(v, inv_r, R.flags, R.seed + base, static_cast<uint64_t>(r) * R.kp + c, sb);
+            uint2 p = encode16<SR>(v, rht, inv_r, R.flags & NVFP4_Q_HI_FIRST, R.seed + base,
+                                   static_cast<uint64_t>(r) * R.kp + c, sb);
             *reinterpret_cast<uint2*>(R.packed + r * (R.kp >> 1) + (c >> 1)) = p;
             row_sc[(gc >> 2) * 512 + (lr & 31) * 16 + (lr >> 5) * 4 + (gc & 3)] = static_cast<uint8_t>(sb);
         }
@@ -339,10 +346,11 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict_
             float v[16];
 #pragma unroll
             for (int l = 0; l < 16; ++l) v[l] = bf16_value(tile[(g * 16 + l) * TILE_PITCH + n]);
-            if (C.flags & NVFP4_Q_RHT) hadamard16(v, sg);
+            const bool rht = C.flags & NVFP4_Q_RHT;
+            if (rht) hadamard16_unscaled(v, sg);
             uint32_t sb;
-            uint2 p = encode16(v, inv_c, C.flags, C.seed + base,
-                               static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16), sb);
+            uint2 p = encode16<SR>(v, rht, inv_c, C.flags & NVFP4_Q_HI_FIRST, C.seed + base,
+                                   static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16), sb);
             *reinterpret_cast<uint2*>(col_out + n * COL_OUT_PITCH + g * 8) = p;
             col_sc[(g >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (g & 3)] = static_cast<uint8_t>(sb);
         }
@@ -361,14 +369,23 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict_
     }
 }
 
+template <int DT, int SR>
+static void launch_tile_sr(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok, const float* signs,
+                           const int32_t* base, const Orient& R, const Orient& C, bool row, bool col, cudaStream_t st) {
+    dim3 grid(static_cast<unsigned>(round128(rows) / 128), static_cast<unsigned>(round128(cols) / 128));
+    if (row && col) quant_tile_kernel<DT, true, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
+    else if (row) quant_tile_kernel<DT, true, false, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
+    else quant_tile_kernel<DT, false, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
+}
+
 template <int DT>
 static int launch_tile(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok,
                        const float* signs, const int32_t* base, const Orient& R, const Orient& C, bool row, bool col,
                        cudaStream_t st) {
-    dim3 grid(static_cast<unsigned>(round128(rows) / 128), static_cast<unsigned>(round128(cols) / 128));
-    if (row && col) quant_tile_kernel<DT, true, true><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
-    else if (row) quant_tile_kernel<DT, true, false><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
-    else quant_tile_kernel<DT, false, true><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
+    const int sr = sr_of_flags(row ? R.flags : C.flags);
+    if (sr == SR_NONE) launch_tile_sr<DT, SR_NONE>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
+    else if (sr == SR_HASH) launch_tile_sr<DT, SR_HASH>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
+    else launch_tile_sr<DT, SR_PHILOX>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
     return launch_status("nvfp4_quantize_tile");
 }
 
@@ -380,7 +397,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
                                                       const uint8_t* __restrict__ scales,
                                                       const float* __restrict__ pts, int64_t kp, int64_t rows,
                                                       int64_t cols, int hi_first, void* __restrict__ out,
-                                                      int64_t out_stride) {
+                                                      int64_t out_stride, int vec_ok) {
     const int64_t gpr = (cols + 15) >> 4;
     const int64_t gi = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (gi >= rows * gpr) return;
@@ -389,15 +406,35 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     const float s = e4m3_to_float(__ldg(scales + scale_offset(r, g, kp >> 4)));
     const float t = __ldg(pts);
     const uint32_t w[2] = {p.x, p.y};
+    float v[16];
 #pragma unroll
     for (int l = 0; l < 16; ++l) {
-        const int64_t c = g * 16 + l;
-        if (c >= cols) break;
-        uint32_t byte = (w[l >> 3] >> (8 * ((l >> 1) & 3))) & 0xffu;
-        uint32_t code = ((l & 1) ^ (hi_first ? 1 : 0)) ? (byte >> 4) : (byte & 15u);
-        float v = __fmul_rn(__fmul_rn(e2m1_to_float(code), s), t);
-        if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[r * out_stride + c] = __float2bfloat16_rn(v);
-        else static_cast<float*>(out)[r * out_stride + c] = v;
+        const uint32_t byte = (w[l >> 3] >> (8 * ((l >> 1) & 3))) & 0xffu;
+        const uint32_t code = ((l & 1) ^ (hi_first ? 1 : 0)) ? (byte >> 4) : (byte & 15u);
+        v[l] = __fmul_rn(__fmul_rn(e2m1_to_float(code), s), t);
+    }
+    const int64_t c0 = g * 16;
+    if (vec_ok && c0 + 16 <= cols) {
+        if constexpr (OUT_BF16) {
+            uint32_t h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = bf16_bits(v[2 * j]) | (static_cast<uint32_t>(bf16_bits(v[2 * j + 1])) << 16);
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + r * out_stride + c0);
+            dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+            dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+        } else {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + r * out_stride + c0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int l = 0; l < 16; ++l) {
+        if (c0 + l < cols) {
+            if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[r * out_stride + c0 + l] = __float2bfloat16_rn(v[l]);
+            else static_cast<float*>(out)[r * out_stride + c0 + l] = v[l];
+        }
     }
 }
 
@@ -457,6 +494,8 @@ extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64
     const int both_sr = NVFP4_Q_SR_HASH | NVFP4_Q_SR_PHILOX;
     NVFP4_REQUIRE((row_flags & both_sr) != both_sr && (col_flags & both_sr) != both_sr, NVFP4_ERR_ARG,
                   "nvfp4_quantize_tile: choose one stochastic rounding source");
+    NVFP4_REQUIRE(!(row && col) || sr_of_flags(row_flags) == sr_of_flags(col_flags), NVFP4_ERR_ARG,
+                  "nvfp4_quantize_tile: both orientations must use the same rounding source");
     const int64_t rp = round128(rows), cp = round128(cols);
     NVFP4_REQUIRE(cp / 128 <= 65535, NVFP4_ERR_ARG, "nvfp4_quantize_tile: more than 65535 column tiles");
     NVFP4_REQUIRE(rp / 128 <= 0x7fffffffLL, NVFP4_ERR_ARG, "nvfp4_quantize_tile: too many row tiles");
@@ -517,7 +556,9 @@ extern "C" int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, co
     const int64_t groups = rows * ((cols + 15) / 16);
     const unsigned blocks = static_cast<unsigned>((groups + 255) / 256);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (out_dtype == NVFP4_BF16) dequant_kernel<true><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride);
-    else dequant_kernel<false><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride);
+    const int esz = out_dtype == NVFP4_BF16 ? 2 : 4;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (out_stride * esz) % 16 == 0;
+    if (out_dtype == NVFP4_BF16) dequant_kernel<true><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride, vec_ok);
+    else dequant_kernel<false><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride, vec_ok);
     return launch_status("nvfp4_dequantize");
 }

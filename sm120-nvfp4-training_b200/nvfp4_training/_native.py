@@ -30,6 +30,7 @@ _SIGNATURES = {
     "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P]),
     "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P]),
     "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
+    "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
 }
 
 
@@ -143,4 +144,42 @@ def dequantize(packed, scales, pts, rows, cols, *, hi_first=False, dtype=torch.f
     with torch.cuda.device(packed.device):
         check(lib().nvfp4_dequantize(packed.data_ptr(), scales.data_ptr(), pts.data_ptr(), packed.shape[1] * 2, rows, cols,
                                      int(hi_first), dtype_code(out), out.data_ptr(), out.stride(0), stream_of(packed)))
+    return out
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Device int32 that kernels with bounded waits raise on expiry; read it with check_status()."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _STATUS.get(idx)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[idx] = buf
+    return buf
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the device status words (tests, check_finite, end of a benchmark)."""
+    for idx, buf in _STATUS.items():
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(buf.item())
+        if code:
+            buf.zero_()
+            raise RuntimeError(f"NVFP4 kernel on cuda:{idx} reported status {code} (bounded device-side wait expired)")
+
+
+def gemm(a, sfa, pts_a, b, sfb, pts_b, *, rows, cols, out_dtype=torch.bfloat16, bias=None, raw_bf16=True, out=None):
+    """out[rows, cols] = crop(A @ B.T) * (pts_a * pts_b) (+ bias); a [M, K/2], b [N, K/2] packed payloads."""
+    M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
+    if b.shape[1] != a.shape[1]:
+        raise ValueError("Packed contraction dimensions do not match")
+    if out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        check(lib().nvfp4_gemm(a.data_ptr(), sfa.data_ptr(), ptr(pts_a), b.data_ptr(), sfb.data_ptr(), ptr(pts_b), M, N, K,
+                               ptr(bias), dtype_code(bias) if bias is not None else 0, out.data_ptr(), dtype_code(out),
+                               out.stride(0), rows, cols, int(bool(raw_bf16)), status_word(a.device).data_ptr(), stream_of(a)))
     return out
