@@ -194,6 +194,85 @@ def matmul_packed(a, b, rows, cols, *, raw_bf16=True, out_bf16=True, bias=None) 
     return rescale(raw, a[2], b[2], rows, cols, raw_bf16=raw_bf16, out_bf16=out_bf16, bias=bias)
 
 
+class AdamCfg(C.Structure):
+    _fields_ = [("n", C.c_int64), ("master", C.c_int), ("vbits", C.c_int), ("m4", C.c_int), ("nonlinear_m", C.c_int),
+                ("block", C.c_int), ("grad_kind", C.c_int), ("grad_cols", C.c_int64), ("grad_stride", C.c_int64),
+                ("sa", C.c_float), ("sb", C.c_float), ("add_extra", C.c_int), ("lr", C.c_float), ("decay", C.c_float),
+                ("b1", C.c_float), ("b2", C.c_float), ("c1", C.c_float), ("c2", C.c_float), ("eps", C.c_float),
+                ("step", C.c_uint32), ("key", C.c_uint32), ("want_amax", C.c_int)]
+
+
+# storage format -> (master, variance bits, momentum bits)   (engine6.py:13-17)
+FORMATS = {"tile32": (32, 16, 8), "fp32_v8": (32, 8, 8), "split24_v16": (24, 16, 8), "split24_v8": (24, 8, 8),
+           "sr16_v8": (16, 8, 8), "half16_v16": (17, 16, 8), "half16_v8": (17, 8, 8), "half16_m8v4": (17, 4, 8),
+           "half16_m4v4": (17, 4, 4), "half16_m4v4_sqrt": (17, 4, 4), "float8_v8": (8, 8, 8),
+           "float8_m4v4_sqrt": (8, 4, 4), "half16_v8b64": (17, 8, 8), "half16_v8b128": (17, 8, 8), "half16_v8b256": (17, 8, 8)}
+
+
+def state_block(fmt: str) -> int:
+    return int(fmt.split("v8b")[1]) if "v8b" in fmt else 512
+
+
+def adam_hyper(lr, betas, eps, weight_decay, t):
+    """The scalar arguments exactly as engine6.py:88-91 computes them (Python doubles, rounded to FP32 at launch)."""
+    import math
+    b1, b2 = betas
+    return dict(lr=lr, decay=1 - lr * weight_decay, b1=b1, b2=b2, c1=1 / (1 - b1 ** t), c2=1 / math.sqrt(1 - b2 ** t), eps=eps)
+
+
+def adam_update(fmt, p, grad, m, v, ms, vs, *, step, key, hyper, tail=None, unit=None, grad_kind=0, grad_cols=1,
+                grad_stride=1, sa=1.0, sb=1.0, extra=None, want_amax=True, master=None):
+    """adam_kernel.update (adam_kernel.py:30-204) in place on numpy arrays; returns per-block amax partials."""
+    mst, vb, mb = FORMATS[fmt]
+    if master is not None:
+        mst = master
+    n = p.size
+    block = state_block(fmt)
+    tiles = (n + block - 1) // block
+    part = np.zeros(tiles, dtype=np.float32)
+    cfg = AdamCfg(n=n, master=mst, vbits=vb, m4=int(mb == 4), nonlinear_m=int(fmt.endswith("_sqrt")), block=block,
+                  grad_kind=grad_kind, grad_cols=grad_cols, grad_stride=grad_stride, sa=sa, sb=sb,
+                  add_extra=int(extra is not None), step=step & 0xFFFFFFFF, key=key & 0xFFFFFFFF, want_amax=int(want_amax),
+                  **{k: float(val) for k, val in hyper.items()})
+    L = lib()
+    L.orc_adam_update.restype = None
+    L.orc_adam_update.argtypes = [C.c_void_p] * 11
+    L.orc_adam_update(C.byref(cfg), _ptr(p), _ptr(grad), _ptr(extra), _ptr(m), _ptr(v), _ptr(ms), _ptr(vs), _ptr(tail),
+                      _ptr(unit), _ptr(part))
+    return part
+
+
+def adam_update_plain(p, g, m, v, hyper):
+    """optimizer_v5._update with FP32 moments (tensors below 4096 elements); returns amax of the BF16-rounded result."""
+    L = lib()
+    L.orc_adam_update_plain.restype = None
+    L.orc_adam_update_plain.argtypes = [C.c_int64] + [C.c_void_p] * 4 + [C.c_float] * 7 + [C.c_void_p]
+    out = np.zeros(1, dtype=np.float32)
+    h = hyper
+    L.orc_adam_update_plain(p.size, _ptr(p), _ptr(g), _ptr(m), _ptr(v), h["lr"], h["decay"], h["b1"], h["b2"], h["c1"],
+                            h["c2"], h["eps"], _ptr(out))
+    return float(out[0])
+
+
+def finish_scale(part: np.ndarray) -> np.float32:
+    L = lib()
+    L.orc_finish_scale.restype = C.c_float
+    L.orc_finish_scale.argtypes = [C.c_void_p, C.c_int64]
+    part = np.ascontiguousarray(part, dtype=np.float32)
+    return np.float32(L.orc_finish_scale(_ptr(part), part.size))
+
+
+def split_init(src: np.ndarray, master: int):
+    L = lib()
+    L.orc_split_init.restype = None
+    L.orc_split_init.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
+    src = np.ascontiguousarray(src, dtype=np.float32)
+    hi = np.empty(src.shape, dtype=np.uint16)
+    tail = np.empty(src.shape, dtype=np.int8) if master == 24 else None
+    L.orc_split_init(_ptr(src), src.size, master, _ptr(hi), _ptr(tail))
+    return hi, tail
+
+
 def philox(ctr, key):
     c = np.asarray(ctr, dtype=np.uint32); k = np.asarray(key, dtype=np.uint32); o = np.empty(4, dtype=np.uint32)
     lib().orc_philox4x32_10(_ptr(c), _ptr(k), _ptr(o))

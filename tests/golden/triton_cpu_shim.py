@@ -7,6 +7,9 @@ reference sources are mounted).  Two gaps of ``TRITON_INTERPRET=1`` are closed:
   rounds to nearest even (PTX ``cvt.rn``).  Casts to bf16 / fp16 / fp8e4nv are redirected to
   PyTorch's CPU conversions, which implement IEEE round-to-nearest-even (and E4M3 saturating
   semantics identical to ``cvt.rn.satfinite`` inside the finite range the kernels use).
+* scalar arguments: the compiled launcher passes a Python float as an FP32 kernel parameter, so
+  expressions such as ``1. - b1`` are FP32 device arithmetic; the stock interpreter keeps the Python
+  double.  Float arguments are turned into FP32 scalars here.
 * inline PTX: the three instructions the reference embeds are given their PTX-ISA meaning:
   ``mul.rn.f32`` (one rounded multiply), ``cvt.rni.s32.f32`` (round half to even to int32) and
   ``cvt.rn.satfinite.e2m1x2.f32`` (two floats to two e2m1 nibbles, nearest, ties to even code,
@@ -99,3 +102,15 @@ def _inline_asm(self, inlineAsm, constraints, values, type, isPure, pack):
 
 
 _interp.InterpreterBuilder.create_inline_asm = _inline_asm
+
+
+_orig_implicit_cvt = _interp._implicit_cvt
+
+
+def _implicit_cvt(arg):
+    if isinstance(arg, float):
+        return tl.tensor(_interp.TensorHandle(np.array([arg], dtype=np.float32), tl.float32), tl.float32)
+    return _orig_implicit_cvt(arg)
+
+
+_interp._implicit_cvt = _implicit_cvt

@@ -1,0 +1,74 @@
+"""The AdamW oracle against golden vectors produced by the reference's own Triton kernels (CPU interpreter)."""
+import numpy as np
+import pytest
+
+import oracle as O
+from conftest import GOLDEN
+
+FORMATS = ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "sr16_v8", "half16_m4v4_sqrt", "float8_m4v4_sqrt", "half16_m8v4"]
+
+
+@pytest.fixture(scope="module")
+def gold():
+    return np.load(GOLDEN / "adamw_reference.npz")
+
+
+def hyper_for(gold, t):
+    lr, b1, b2, eps, wd = (float(x) for x in gold["hyper"])
+    return O.adam_hyper(lr, (b1, b2), eps, wd, t)
+
+
+def run_oracle_steps(gold, fmt, check):
+    master, vb, mb = O.FORMATS[fmt]
+    rows, cols, stride = (int(x) for x in gold["meta"])
+    n = rows * cols
+    width = O.state_block(fmt)
+    p = gold[f"{fmt}_p0"].copy()
+    tail = gold[f"{fmt}_tail0"].copy() if master == 24 else None
+    unit = gold[f"{fmt}_unit0"].copy() if master == 8 else None
+    m = np.zeros((n + 1) // 2 if mb == 4 and vb != 4 else n, dtype=np.uint8 if mb == 4 else np.int8)
+    ms = np.zeros(-(-n // (64 if mb == 4 else width)), dtype=np.float32)
+    vs = np.zeros(-(-n // (64 if vb == 4 else width)), dtype=np.float32)
+    v = None
+    if vb != 4 or mb != 4:
+        v = np.zeros(-(-n // 2) if vb == 4 else n, dtype=np.uint8 if vb < 16 else np.uint16)
+    sa, sb = (float(x) for x in gold["scales"])
+    for t in (1, 2, 3):
+        packed = t < 3
+        grad = gold[f"raw{t - 1}"] if packed else gold["dense"]
+        part = O.adam_update(fmt, p, grad, m, v, ms, vs, step=t, key=12345 + 7919 * 3, hyper=hyper_for(gold, t), tail=tail,
+                             unit=unit, grad_kind=2 if packed else 0, grad_cols=cols if packed else 1,
+                             grad_stride=stride if packed else 1, sa=sa, sb=sb, extra=gold["extra"] if t == 2 else None)
+        check(t, dict(p=p, m=m, v=v, ms=ms, vs=vs, tail=tail, unit=unit, part=part, scale=np.array([O.finish_scale(part)])))
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_update_matches_reference(gold, fmt):
+    def check(t, state):
+        for name, got in state.items():
+            if got is None:
+                continue
+            want = gold[f"{fmt}_s{t}_{name}"]
+            same = np.array_equal(got.view(np.uint8) if got.dtype != np.uint8 else got, want.view(np.uint8) if want.dtype != np.uint8 else want)
+            assert same, f"{fmt} step {t} {name}: {(got != want).sum()} of {got.size} differ"
+    run_oracle_steps(gold, fmt, check)
+
+
+def test_split_init_matches_reference(gold):
+    w0 = gold["w0"]
+    hi, _ = O.split_init(w0, 17)
+    assert np.array_equal(hi, gold["half16_v8_p0"])
+    hi, tail = O.split_init(w0, 24)
+    assert np.array_equal(hi, gold["split24_v8_p0"]) and np.array_equal(tail, gold["split24_v8_tail0"])
+    hi, _ = O.split_init(w0, 16)
+    assert np.array_equal(hi, gold["sr16_v8_p0"])
+
+
+def test_plain_small_tensor_path_matches_reference(gold):
+    p, g = gold["plain_p0"].copy(), gold["plain_g"]
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    for t in (1, 2):
+        amax = O.adam_update_plain(p, g, m, v, hyper_for(gold, t))
+        for name, got in (("p", p), ("m", m), ("v", v)):
+            assert np.array_equal(got.view(np.uint32), gold[f"plain_s{t}_{name}"].view(np.uint32)), (t, name)
+        assert np.float32(amax) == gold[f"plain_s{t}_part"].max()
