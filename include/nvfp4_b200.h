@@ -117,6 +117,44 @@ int nvfp4_gemm(const uint8_t* a, const uint8_t* sfa, const float* pts_a, const u
                const float* pts_b, int64_t M, int64_t N, int64_t K, const void* bias, int bias_dtype, void* out,
                int out_dtype, int64_t ldo, int64_t rows, int64_t cols, int raw_bf16, int* status, nvfp4_stream_t stream);
 
+/*
+ * Compressed AdamW step, one kernel per parameter tensor (n elements, flat):
+ *   decode master + moments -> m = b1 m + (1-b1) g, v = b2 v + (1-b2) g g,
+ *   p = p * decay - (lr c1) m / (sqrt(v) c2 + eps) -> re-encode -> amax of bf16(p) -> next tensor scale.
+ * master: 32 FP32 | 24 BF16 head + int8 `tail` | 17 FP16, stochastically rounded | 16 BF16, stochastically rounded |
+ *         8 E4M3 times the power-of-two `unit` of each 512 weights (units grow when an update would overflow).
+ * moments: mbits 8 = int8 m with FP32 scale per state block; mbits 4 = nibble code (sqrt-coded if nonlinear_m) with
+ *          scales per 64; vbits 16 = FP16 v / scale, 8 = uint8 code of sqrt(v), 4 = nibble code of sqrt(v) with scales
+ *          per 64 (mbits = vbits = 4: one byte per element in `m`, m low nibble, and `v` is unused).
+ * grad_kind: 0 FP32, 1 BF16, 2 raw BF16 GEMM output [*, grad_stride] scaled as bf16(raw * bf16(sa[0] * sb[0])).
+ * extra: nullable FP32 gradient added after the decode.  grad_mul: factor applied to the gradient when != 1 (data-
+ * parallel averaging).  decay = 1 - lr * weight_decay, c1 = 1 / (1 - b1^t), c2 = 1 / sqrt(1 - b2^t), step = t;
+ * ctrl: nullable device float[4] = (c1, c2, -, bits of t) read on the device instead (CUDA-graph replay).
+ * key: per-parameter stream of the counter-based rounding bits.  scale_out: nullable device float that receives
+ * max(amax, 1e-12) / 2688-by-multiplication, the tensor scale of the next forward; needs `scratch` (the amax scratch).
+ * Replaces the Triton kernels adam_kernel.update (src/nvfp4_training/_backend/adam_kernel.py:30-204) and
+ * optimizer_v5._partial_max/_finish_scale (optimizer_v5.py:55-64) as launched by AdamW6._update_param
+ * (engine6.py:44-104), and master8.round_e4m3 (master8.py:25-34).
+ */
+int nvfp4_adamw_step(void* p, int master, const void* grad, int grad_kind, int64_t grad_cols, int64_t grad_stride,
+                     const float* sa, const float* sb, const float* extra, float grad_mul, void* m, void* v, float* ms,
+                     float* vs, int8_t* tail, float* unit, int64_t n, int vbits, int mbits, int nonlinear_m, int state_block,
+                     float lr, float decay, float b1, float b2, float c1, float c2, float eps, uint32_t step, uint32_t key,
+                     const float* ctrl, float* scale_out, void* scratch, nvfp4_stream_t stream);
+
+/*
+ * AdamW with FP32 master and FP32 moments for tensors below 4096 elements (norm gains, biases).
+ * Replaces optimizer_v5._update with COMPACT = False (src/nvfp4_training/_backend/optimizer_v5.py:9-53).
+ */
+int nvfp4_adamw_plain(float* p, const float* grad, float* m, float* v, int64_t n, float grad_mul, float lr, float decay,
+                      float b1, float b2, float c1, float c2, float eps, const float* ctrl, nvfp4_stream_t stream);
+
+/*
+ * FP32 weights -> master storage: FP16 (master 17) or BF16 (16, 24) head, plus the signed int8 residual for 24.
+ * Replaces adam_kernel.split_init (src/nvfp4_training/_backend/adam_kernel.py:21-28).
+ */
+int nvfp4_split_init(const float* src, int64_t n, int master, void* hi, int8_t* tail, nvfp4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,7 @@
 
     python build.py [--force] [--verbose]
 
+A source file may name extra compiler flags on its first line (`// nvcc-flags: --fmad=false`).
 nvcc cross-compiles without a GPU; the shared object is loaded with ctypes by nvfp4_training._native.
 """
 from __future__ import annotations
@@ -50,7 +51,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc, *ARCH, *COMMON, "-c", str(src), "-o", str(obj)]
+            first = src.read_text().splitlines()[0]
+            extra = first.split("nvcc-flags:", 1)[1].split() if "nvcc-flags:" in first else []
+            cmd = [nvcc, *ARCH, *COMMON, *extra, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -30,6 +30,10 @@ _SIGNATURES = {
     "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P]),
     "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P]),
     "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
+    "nvfp4_adamw_step": (I32, [P, I32, P, I32, I64, I64, P, P, P, F, P, P, P, P, P, P, I64, I32, I32, I32, I32,
+                                 F, F, F, F, F, F, F, U32, U32, P, P, P, P]),
+    "nvfp4_adamw_plain": (I32, [P, P, P, P, I64, F, F, F, F, F, F, F, F, P, P]),
+    "nvfp4_split_init": (I32, [P, I64, I32, P, P, P]),
     "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
 }
 
@@ -183,3 +187,35 @@ def gemm(a, sfa, pts_a, b, sfb, pts_b, *, rows, cols, out_dtype=torch.bfloat16, 
                                ptr(bias), dtype_code(bias) if bias is not None else 0, out.data_ptr(), dtype_code(out),
                                out.stride(0), rows, cols, int(bool(raw_bf16)), status_word(a.device).data_ptr(), stream_of(a)))
     return out
+
+
+def adamw_step(p, master, grad, m, v, ms, vs, *, vbits, mbits, nonlinear_m, state_block, hyper, step, key, grad_kind=None,
+               grad_cols=1, grad_stride=1, sa=None, sb=None, extra=None, grad_mul=1.0, tail=None, unit=None, ctrl=None,
+               scale_out=None):
+    """In-place compressed AdamW on one flat parameter tensor (see nvfp4_adamw_step)."""
+    if grad_kind is None:
+        grad_kind = 0 if grad.dtype == torch.float32 else 1
+    dev = p.device
+    with torch.cuda.device(dev):
+        check(lib().nvfp4_adamw_step(p.data_ptr(), master, grad.data_ptr(), grad_kind, grad_cols, grad_stride, ptr(sa), ptr(sb),
+                                     ptr(extra), float(grad_mul), m.data_ptr(), ptr(v), ms.data_ptr(), vs.data_ptr(), ptr(tail),
+                                     ptr(unit), p.numel(), vbits, mbits, int(bool(nonlinear_m)), state_block, hyper["lr"],
+                                     hyper["decay"], hyper["b1"], hyper["b2"], hyper["c1"], hyper["c2"], hyper["eps"],
+                                     int(step) & 0xFFFFFFFF, int(key) & 0xFFFFFFFF, ptr(ctrl), ptr(scale_out),
+                                     scratch(dev).data_ptr(), stream_of(p)))
+
+
+def adamw_plain(p, grad, m, v, *, hyper, grad_mul=1.0, ctrl=None):
+    with torch.cuda.device(p.device):
+        check(lib().nvfp4_adamw_plain(p.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), float(grad_mul),
+                                      hyper["lr"], hyper["decay"], hyper["b1"], hyper["b2"], hyper["c1"], hyper["c2"],
+                                      hyper["eps"], ptr(ctrl), stream_of(p)))
+
+
+def split_init(src, master):
+    """FP32 tensor -> (head, tail): FP16 head for master 17, BF16 for 16 / 24 (tail only for 24)."""
+    hi = torch.empty_like(src, dtype=torch.float16 if master == 17 else torch.bfloat16)
+    tail = torch.empty_like(src, dtype=torch.int8) if master == 24 else None
+    with torch.cuda.device(src.device):
+        check(lib().nvfp4_split_init(src.data_ptr(), src.numel(), master, hi.data_ptr(), ptr(tail), stream_of(src)))
+    return hi, tail
