@@ -4,17 +4,20 @@
 //   A: e2m1 payload [M][K/2] (K-major), SFA: ue4m3, one per 16 elements, in 128-row x 4-scale blocks of
 //      512 bytes ordered [M/128][K/64]; B, SFB likewise with N rows.  M, N, K are multiples of 128.
 //
-// Structure (one persistent CTA per SM, 192 threads):
-//   warp 0   : TMA producer.  Per k-tile of 256 elements: A box 128 rows x 128 B, B box BN rows x 128 B
-//              (both 128-byte swizzled) and the scale blocks as plain bulk copies, all completing on one
-//              mbarrier per stage.  Plain loads only: every CTA fetches its own tiles.
-//   warp 1   : allocates TMEM; one lane issues tcgen05.cp (scale blocks smem -> TMEM) and
-//              tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N x K64) and commits to the stage's
-//              "empty" barrier / the accumulator's "full" barrier.
-//   warps 2-5: epilogue; each owns the 32 TMEM lanes of its sub-partition: tcgen05.ld -> scale -> cast ->
-//              global stores, then releases the accumulator.
-// Every wait is bounded: on expiry the kernel raises the status word, all roles leave their loops, the
-// producer waits (bounded) for loads still in flight, TMEM is freed and the kernel returns.
+// One persistent CTA per SM, 320 threads, warp-specialised:
+//   warp 0    TMA producer.  Per k-tile of 256 elements: A box 128 rows x 128 B and B box BN rows x 128 B (128-byte
+//             swizzle) plus the scale blocks as plain bulk copies, all completing on the stage's mbarrier.  Plain
+//             loads only: every CTA fetches its own tiles.
+//   warp 1    allocates TMEM; one lane issues tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N x K64) and commits
+//             to the stage / scale-buffer / accumulator barriers.
+//   warps 2-5 scale-factor movers: read the stage's scale blocks from shared memory and write them into the TMEM
+//             scale buffers with tcgen05.st (each warp fills the 32 lanes of its own sub-partition, which is the
+//             four-fold replication the MMA expects).  This keeps scale traffic out of the MMA issue pipe.
+//   warps 6-9 epilogue: tcgen05.ld -> scale / cast -> swizzled shared staging -> TMA store (which also crops).
+//             With BN = 256 the single accumulator is handed back in two halves so the next tile's first MMAs
+//             start while the second half is still being drained.
+// Every wait is bounded: on expiry the kernel raises the status word, all roles leave their loops, the producer
+// waits (bounded) for loads still in flight, TMEM is freed and the kernel returns.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -23,11 +26,12 @@
 
 namespace nvfp4 {
 
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;
 constexpr int BM = 128;
 constexpr int BK = 256;             // elements per k-tile = 128 payload bytes per row
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int SF_BLOCK = 512;       // 128 rows x 4 scales
+constexpr int EPI_SLAB_BYTES = 2048;  // 32 rows x 64 bytes per epilogue warp and buffer
 constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
 template <int BN> struct GemmCfg {
@@ -37,14 +41,21 @@ template <int BN> struct GemmCfg {
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;
+    static constexpr int HALVES = (BN == 256) ? 2 : 1;   // parts an accumulator is released in
     static constexpr int SFA_COLS = 16;             // 4 k-blocks x 4 columns
     static constexpr int SFB_COLS = 4 * (BN / 32);  // 4 k-blocks x BN/32 columns
     static constexpr int ACC_COLS = ACC_STAGES * BN;
-    static constexpr int SF_BASE = ACC_COLS;        // two scale buffers (even / odd k-tile) behind the accumulators
+    static constexpr int SF_BUFS = 3;
+    static constexpr int SF_BASE = ACC_COLS;
     static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static_assert(ACC_COLS + 2 * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
+    static constexpr int EPI_BUFS = 1;              // staging slabs per epilogue warp
+    static constexpr int EPI_BYTES = 4 * EPI_BUFS * EPI_SLAB_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * SF_BUFS + ACC_STAGES + ACC_STAGES * HALVES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static_assert(ACC_COLS + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
+    static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 struct GemmArgs {
@@ -56,7 +67,7 @@ struct GemmArgs {
     void* out;
     int* status;         // null or device int, set non-zero when a bounded wait expired
     int64_t ldo;
-    int bias_f32, out_f32, raw_bf16;
+    int bias_f32, out_f32, raw_bf16, tma_store;
     int M, N, K, rows, cols;
     int tiles_m, tiles_n, k_tiles;
 };
@@ -96,13 +107,18 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(src)) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
 }
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
                                        uint32_t tmem_sfa, uint32_t tmem_sfb) {
@@ -121,35 +137,54 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 
 // K-major, 128-byte swizzled operand tile (rows of 128 bytes, 8-row groups 1024 bytes apart).
 __device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
     return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-// One 512-byte scale block seen as 32 rows x 16 bytes, unswizzled (8-row groups 128 bytes apart).
-__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
-    return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (8ull << 32) | (1ull << 46);
+__device__ __forceinline__ uint32_t instr_desc(int n) {  // e2m1 x e2m1, ue4m3 scales, K-major A and B, M = 128
+    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 }
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_out, const GemmArgs g) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint8_t* epi_smem = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
     uint64_t* full = bars;
-    uint64_t* empty = bars + Cfg::STAGES;
-    uint64_t* acc_full = bars + 2 * Cfg::STAGES;
-    uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + Cfg::ACC_STAGES);
+    uint64_t* empty = full + Cfg::STAGES;
+    uint64_t* sf_full = empty + Cfg::STAGES;
+    uint64_t* sf_empty = sf_full + Cfg::SF_BUFS;
+    uint64_t* acc_full = sf_empty + Cfg::SF_BUFS;
+    uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;  // [ACC_STAGES][HALVES]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + Cfg::ACC_STAGES * Cfg::HALVES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < Cfg::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
+        for (int s = 0; s < Cfg::SF_BUFS; ++s) { mbar_init(&sf_full[s], 4); mbar_init(&sf_empty[s], 1); }
+        for (int a = 0; a < Cfg::ACC_STAGES; ++a) mbar_init(&acc_full[a], 1);
+        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -162,6 +197,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = g.tiles_m * g.tiles_n;
+    const int kb_total = g.K / 64;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -174,14 +210,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int kt = 0; kt < g.k_tiles; ++kt) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = smem + stage * Cfg::STAGE_BYTES;
-                    const int kblocks = min(4, g.K / 64 - kt * 4);
+                    const int kblocks = min(4, kb_total - kt * 4);
                     const uint32_t sf_bytes = kblocks * SF_BLOCK;
                     mbar_expect_tx(&full[stage], A_STAGE_BYTES + Cfg::B_STAGE_BYTES + sf_bytes * (1 + BN / 128));
                     tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[stage]);
                     tma_load_2d(st + A_STAGE_BYTES, &map_b, kt * 128, tn * BN, &full[stage]);
-                    const int64_t kb_total = g.K / 64;
-                    bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES, g.sfa + (static_cast<int64_t>(tm) * kb_total + kt * 4) * SF_BLOCK,
-                              sf_bytes, &full[stage]);
+                    bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES,
+                              g.sfa + (static_cast<int64_t>(tm) * kb_total + kt * 4) * SF_BLOCK, sf_bytes, &full[stage]);
 #pragma unroll
                     for (int nb = 0; nb < BN / 128; ++nb)
                         bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES + Cfg::SFA_STAGE_BYTES + nb * 4 * SF_BLOCK,
@@ -205,54 +240,107 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            const uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            const uint32_t idesc_full = instr_desc(BN), idesc_half = instr_desc(BN / 2);
             int stage = 0; uint32_t phase = 0;
+            int sfb = 0; uint32_t sf_phase = 0;
             int local = 0;
-            uint32_t ktile_count = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
                 const int acc = local % Cfg::ACC_STAGES;
                 const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
-                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + acc * BN;
-                for (int kt = 0; kt < g.k_tiles; ++kt, ++ktile_count) {
-                    if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                for (int kt = 0; kt < g.k_tiles; ++kt) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag) || !mbar_wait(&sf_full[sfb], sf_phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
                     const uint32_t sb = sa + A_STAGE_BYTES;
-                    const uint32_t ssfa = sb + Cfg::B_STAGE_BYTES;
-                    const uint32_t ssfb = ssfa + Cfg::SFA_STAGE_BYTES;
-                    const uint32_t sf_tmem = tmem_base + Cfg::SF_BASE + (ktile_count & 1) * Cfg::SF_BUF_COLS;
-                    const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + Cfg::SFA_COLS;
-                    const int kblocks = min(4, g.K / 64 - kt * 4);
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        tc_cp_sf(sfa_tmem + kb * 4, scale_desc(ssfa + kb * SF_BLOCK));
+                    const uint32_t sfa_tmem = tmem_base + Cfg::SF_BASE + sfb * Cfg::SF_BUF_COLS;
+                    const uint32_t sfb_tmem = sfa_tmem + Cfg::SFA_COLS;
+                    const int kblocks = min(4, kb_total - kt * 4);
+                    if (kt == 0) {
+                        // first k-tile: the accumulator comes back from the epilogue in HALVES parts
 #pragma unroll
-                        for (int nb = 0; nb < BN / 128; ++nb)
-                            tc_cp_sf(sfb_tmem + kb * (BN / 32) + nb * 4, scale_desc(ssfb + (nb * 4 + kb) * SF_BLOCK));
-                    }
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        tc_mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc,
-                               (kt > 0 || kb > 0) ? 1u : 0u, sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
+                        for (int h = 0; h < Cfg::HALVES; ++h) {
+                            if (!mbar_wait(&acc_empty[acc * Cfg::HALVES + h], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                            tc_fence_after();
+                            constexpr int NH = BN / Cfg::HALVES;
+                            for (int kb = 0; kb < kblocks; ++kb)
+                                tc_mma(tmem_acc + h * NH, operand_desc(sa + kb * 32), operand_desc(sb + h * NH * 128 + kb * 32),
+                                       Cfg::HALVES == 2 ? idesc_half : idesc_full, kb > 0 ? 1u : 0u, sfa_tmem + kb * 4,
+                                       sfb_tmem + kb * (BN / 32) + h * (NH / 32));
+                        }
+                        if (!ok) break;
+                    } else {
+                        for (int kb = 0; kb < kblocks; ++kb)
+                            tc_mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, 1u,
+                                   sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
                     }
                     tc_commit(&empty[stage]);
+                    tc_commit(&sf_empty[sfb]);
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                    if (++sfb == Cfg::SF_BUFS) { sfb = 0; sf_phase ^= 1; }
                 }
                 if (ok) tc_commit(&acc_full[acc]);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------ scale-factor movers -------------------------
+        const int sub = warp & 3;
+        const uint32_t lane_field = static_cast<uint32_t>(sub * 32) << 16;
+        int stage = 0; uint32_t phase = 0;
+        int sfb = 0; uint32_t sf_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int kt = 0; kt < g.k_tiles; ++kt) {
+                if (!mbar_wait(&full[stage], phase, abort_flag) || !mbar_wait(&sf_empty[sfb], sf_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint8_t* ssfa = smem + stage * Cfg::STAGE_BYTES + A_STAGE_BYTES + Cfg::B_STAGE_BYTES;
+                const uint8_t* ssfb = ssfa + Cfg::SFA_STAGE_BYTES;
+                const uint32_t sfa_tmem = tmem_base + lane_field + Cfg::SF_BASE + sfb * Cfg::SF_BUF_COLS;
+                const uint32_t sfb_tmem = sfa_tmem + Cfg::SFA_COLS;
+                // lane l holds, per k-block, the 16 bytes of rows l, 32 + l, 64 + l, 96 + l: four TMEM columns
+                uint32_t r[16];
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(ssfa + kb * SF_BLOCK + lane * 16);
+                    r[4 * kb] = q.x; r[4 * kb + 1] = q.y; r[4 * kb + 2] = q.z; r[4 * kb + 3] = q.w;
+                }
+                tc_st16(sfa_tmem, r);
+#pragma unroll
+                for (int part = 0; part < BN / 128; ++part) {
+                    // 16 consecutive columns: with BN = 256 two k-blocks of 8 columns (row block 0 then 1), else four of 4
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        int kb, nb;
+                        if (BN == 256) { kb = 2 * part + (i >> 1); nb = i & 1; } else { kb = i; nb = 0; }
+                        const uint4 q = *reinterpret_cast<const uint4*>(ssfb + (nb * 4 + kb) * SF_BLOCK + lane * 16);
+                        r[4 * i] = q.x; r[4 * i + 1] = q.y; r[4 * i + 2] = q.z; r[4 * i + 3] = q.w;
+                    }
+                    tc_st16(sfb_tmem + part * 16, r);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&sf_full[sfb]); mbar_arrive(&empty[stage]); }
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                if (++sfb == Cfg::SF_BUFS) { sfb = 0; sf_phase ^= 1; }
             }
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int sub = warp & 3;                 // TMEM sub-partition this warp may read
         const int row_in_tile = sub * 32 + lane;
+        uint8_t* slab = epi_smem + (warp - 6) * Cfg::EPI_BUFS * EPI_SLAB_BYTES;
         float alpha = 1.f;
         const bool scaled = g.pts_a != nullptr;
         if (scaled) {
             alpha = __fmul_rn(__ldg(g.pts_a), __ldg(g.pts_b));
             if (g.raw_bf16) alpha = bf16_value(bf16_bits(alpha));
         }
-        int local = 0;
+        const __nv_bfloat162 alpha2 = __float2bfloat162_rn(alpha);
+        const int cols_per_slab = g.out_f32 ? 16 : 32;
+        const int nslab = BN / cols_per_slab;
+        int local = 0, buf = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
             const int tm = t % g.tiles_m, tn = t / g.tiles_m;
@@ -263,71 +351,110 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int64_t row = static_cast<int64_t>(tm) * BM + row_in_tile;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int s = 0; s < nslab; ++s) {
+                const int c0 = s * cols_per_slab;
                 uint32_t r[32];
-                tc_ld32(taddr + c0, r);
+                if (g.out_f32) tc_ld16(taddr + c0, r); else tc_ld32(taddr + c0, r);
                 tc_wait_ld();
+                if (Cfg::HALVES == 2 && (s + 1) * 2 == nslab) {   // the first half of the accumulator has been read out
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES]);
+                }
                 const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
-                if (row < g.rows && col0 < g.cols) {
+                const bool live = col0 < g.cols && static_cast<int64_t>(tm) * BM + sub * 32 < g.rows;
+                if (!live) continue;   // warp-uniform: the whole slab lies outside the crop
+                // ---- value chain -> 64 bytes per row, as 4 x 16 bytes ----
+                uint4 q[4];
+                if (!g.bias && g.raw_bf16 && !g.out_f32) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                        if (scaled) p = __hmul2(p, alpha2);   // bf16 x bf16 is exact in FP32: one rounding, as in the FP32 chain
+                        w[j] = *reinterpret_cast<uint32_t*>(&p);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) q[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                } else {
                     float v[32];
+                    const int nv = cols_per_slab;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(r[j]);
-                        if (g.raw_bf16) x = bf16_value(bf16_bits(x));
-                        if (scaled) {
-                            x = __fmul_rn(x, alpha);
+                        v[j] = 0.f;
+                        if (j < nv) {
+                            float x = __uint_as_float(r[j]);
                             if (g.raw_bf16) x = bf16_value(bf16_bits(x));
-                        }
-                        v[j] = x;
-                    }
-                    if (g.bias) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (col0 + j < g.cols) {
+                            if (scaled) {
+                                x = __fmul_rn(x, alpha);
+                                if (g.raw_bf16) x = bf16_value(bf16_bits(x));
+                            }
+                            if (g.bias && col0 + j < g.cols) {
                                 float b = g.bias_f32 ? __ldg(static_cast<const float*>(g.bias) + col0 + j)
                                                      : bf16_value(__ldg(static_cast<const uint16_t*>(g.bias) + col0 + j));
                                 if (g.raw_bf16) b = bf16_value(bf16_bits(b));
-                                float y = __fadd_rn(v[j], b);
-                                if (g.raw_bf16) y = bf16_value(bf16_bits(y));
-                                v[j] = y;
+                                x = __fadd_rn(x, b);
+                                if (g.raw_bf16) x = bf16_value(bf16_bits(x));
                             }
+                            v[j] = x;
                         }
                     }
-                    const bool full_chunk = col0 + 32 <= g.cols;
                     if (g.out_f32) {
-                        float* dst = static_cast<float*>(g.out) + row * g.ldo + col0;
-                        if (full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) if (col0 + j < g.cols) dst[j] = v[j];
-                        }
+                        for (int j = 0; j < 4; ++j)
+                            q[j] = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
+                                              __float_as_uint(v[4 * j + 3]));
                     } else {
-                        uint16_t* dst = static_cast<uint16_t*>(g.out) + row * g.ldo + col0;
-                        if (full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 u;
-                                u.x = bf16_bits(v[8 * j]) | (uint32_t(bf16_bits(v[8 * j + 1])) << 16);
-                                u.y = bf16_bits(v[8 * j + 2]) | (uint32_t(bf16_bits(v[8 * j + 3])) << 16);
-                                u.z = bf16_bits(v[8 * j + 4]) | (uint32_t(bf16_bits(v[8 * j + 5])) << 16);
-                                u.w = bf16_bits(v[8 * j + 6]) | (uint32_t(bf16_bits(v[8 * j + 7])) << 16);
-                                reinterpret_cast<uint4*>(dst)[j] = u;
+                        for (int j = 0; j < 4; ++j) {
+                            q[j].x = bf16_bits(v[8 * j]) | (uint32_t(bf16_bits(v[8 * j + 1])) << 16);
+                            q[j].y = bf16_bits(v[8 * j + 2]) | (uint32_t(bf16_bits(v[8 * j + 3])) << 16);
+                            q[j].z = bf16_bits(v[8 * j + 4]) | (uint32_t(bf16_bits(v[8 * j + 5])) << 16);
+                            q[j].w = bf16_bits(v[8 * j + 6]) | (uint32_t(bf16_bits(v[8 * j + 7])) << 16);
+                        }
+                    }
+                }
+                if (g.tma_store) {
+                    uint8_t* dst = slab + buf * EPI_SLAB_BYTES;
+                    if (lane == 0) bulk_wait_read<Cfg::EPI_BUFS - 1>();   // the store that last read this buffer has drained it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)   // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
+                        *reinterpret_cast<uint4*>(dst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q[j];
+                    fence_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_out, static_cast<int>(col0), tm * BM + sub * 32, dst);
+                        bulk_commit();
+                    }
+                    if (++buf == Cfg::EPI_BUFS) buf = 0;
+                } else if (row < g.rows) {
+                    // unaligned output: plain stores, element-wise at the ragged edge
+                    const int esz = g.out_f32 ? 4 : 2;
+                    uint8_t* dst = static_cast<uint8_t*>(g.out) + (row * g.ldo + col0) * esz;
+                    if (col0 + cols_per_slab <= g.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = q[j];
+                    } else {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { w[4 * j] = q[j].x; w[4 * j + 1] = q[j].y; w[4 * j + 2] = q[j].z; w[4 * j + 3] = q[j].w; }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < cols_per_slab && col0 + j < g.cols) {
+                                if (g.out_f32) reinterpret_cast<uint32_t*>(dst)[j] = w[j & 15];
+                                else reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
                             }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) if (col0 + j < g.cols) dst[j] = bf16_bits(v[j]);
                         }
                     }
                 }
             }
-            // all of this warp's TMEM reads have completed (wait::ld above): hand the accumulator back
+            // every TMEM read of this warp has completed (wait::ld above): hand the rest of the accumulator back
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + Cfg::HALVES - 1]);
         }
+        if (lane == 0) bulk_wait_all();
     }
 
     tc_fence_before();
@@ -366,8 +493,22 @@ static bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, i
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Output map for the epilogue's stores: boxes of 32 rows x 64 bytes, 64-byte swizzle; the bounds crop the tile.
+static bool make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldo, bool f32) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const int esz = f32 ? 4 : 2;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo * esz)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(64 / esz), 32};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& g, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, GemmArgs& g, cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
     static bool configured[64] = {};
     int dev = 0;
@@ -382,7 +523,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& g
     const int sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
     g.tiles_n = g.N / BN;
     const int grid = std::min(g.tiles_m * g.tiles_n, sms);
-    gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, g);
+    gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, mo, g);
     return launch_status("nvfp4_gemm");
 }
 
@@ -411,9 +552,14 @@ extern "C" int nvfp4_gemm(const uint8_t* a, const uint8_t* sfa, const float* pts
     g.rows = static_cast<int>(rows); g.cols = static_cast<int>(cols);
     g.tiles_m = g.M / BM; g.k_tiles = (g.K + BK - 1) / BK;
     const int bn = (N % 256 == 0) ? 256 : 128;
-    CUtensorMap ma, mb;
+    const int esz = g.out_f32 ? 4 : 2;
+    // the bulk-tensor store needs a 16-byte aligned base and row pitch; anything else takes the plain-store epilogue
+    g.tma_store = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo * esz) % 16 == 0;
+    CUtensorMap ma, mb, mo;
     NVFP4_REQUIRE(make_operand_map(&ma, a, M, K, BM) && make_operand_map(&mb, b, N, K, bn), NVFP4_ERR_LAUNCH,
                   "nvfp4_gemm: cuTensorMapEncodeTiled failed or is unavailable");
+    if (g.tma_store && !make_out_map(&mo, out, rows, cols, ldo, g.out_f32)) g.tma_store = 0;
+    if (!g.tma_store) mo = ma;  // unused by the kernel in this mode, but the parameter must hold a valid map
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    return bn == 256 ? launch_gemm<256>(ma, mb, g, st) : launch_gemm<128>(ma, mb, g, st);
+    return bn == 256 ? launch_gemm<256>(ma, mb, mo, g, st) : launch_gemm<128>(ma, mb, mo, g, st);
 }
