@@ -1,0 +1,184 @@
+"""Packed NVFP4 operands and the launchers around the C-ABI kernels.
+
+Mirrors the operator surface of the reference's src/nvfp4_training/_backend/nvfp4_fast_v2.py (Packed, quantize,
+matmul_packed, stats / SR seed counter), act_pair.py (dual), pair.py (pair), remat.py (single) and scale6.py (matmul):
+same names, argument meaning, counters and exceptions; the kernels behind them are the sm_100a ones.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _native as nat
+
+_SIGNS: dict = {}
+_SEED = 0
+_STATS = {"fp4_gemm": 0, "quant": 0, "sr_quant": 0, "rht_quant": 0, "reused_weight_amax": 0,
+          "packed_activation_saved": 0, "deferred_wgrad": 0, "optimizer_scale_hits": 0, "v5_pair": 0}
+
+
+def sr_flag() -> int:
+    """Stochastic-rounding source: the reference's integer hash (default) or Philox4x32-10 (NVFP4_SR_RNG=philox)."""
+    return nat.Q_SR_PHILOX if os.environ.get("NVFP4_SR_RNG", "hash").lower() == "philox" else nat.Q_SR_HASH
+
+
+def ensure_verified_modes() -> dict:
+    """The reference gates its backend on a per-GPU verification file (nvfp4_fast_v2.py:101-121); this backend is
+    checked by its test-suite against the CPU oracle instead and always runs the paired-weight mode."""
+    return {"aligned": "fast_pair", "irregular": "fast_pair"}
+
+
+def reset_stats(seed: int = 0) -> None:
+    global _SEED
+    _SEED = int(seed)
+    for key in _STATS:
+        _STATS[key] = 0
+
+
+def stats() -> dict:
+    return dict(_STATS)
+
+
+def round128(n: int) -> int:
+    if n <= 0:
+        raise ValueError("Empty dimensions are not supported")
+    return (n + 127) // 128 * 128
+
+
+def get_signs(device) -> torch.Tensor:
+    """16 random +-1 floats from a CPU generator seeded with 1 (nvfp4_fast_v2.py:145-150)."""
+    device = torch.device(device)
+    if device not in _SIGNS:
+        gen = torch.Generator(device="cpu").manual_seed(1)
+        _SIGNS[device] = (torch.randint(0, 2, (16,), generator=gen).float() * 2 - 1).to(device)
+    return _SIGNS[device]
+
+
+@dataclass
+class Packed:
+    data: torch.Tensor   # uint8 [rows_p, cols_p / 2], low nibble = even element
+    scale: torch.Tensor  # uint8 swizzled E4M3 block scales [rows_p / 128 * 32, cols_p / 64 * 16]
+    pts: torch.Tensor    # FP32 tensor scale (device scalar)
+    dtype: torch.dtype   # dtype of the source, decides the GEMM's raw rounding
+
+    @property
+    def shape(self):
+        return (self.data.shape[0], self.data.shape[1] * 2)
+
+
+def _buffers(rows_p, cols_p, device):
+    data = torch.empty((rows_p, cols_p // 2), dtype=torch.uint8, device=device)
+    scale = torch.empty((rows_p // 128 * 32, cols_p // 64 * 16), dtype=torch.uint8, device=device)
+    return data, scale
+
+
+def quantize(x: torch.Tensor, *, sr: bool = False, rht: bool = False, signs: Optional[torch.Tensor] = None,
+             seed: Optional[int] = None, pts: Optional[torch.Tensor] = None, base: Optional[torch.Tensor] = None) -> Packed:
+    """Quantise a 2-D CUDA tensor (any non-negative strides), virtually zero-padded to multiples of 128.
+    `pts` reuses a tensor scale; `base` is the device-resident SR seed offset of graph replays."""
+    global _SEED
+    if x.ndim != 2 or x.device.type != "cuda":
+        raise ValueError("quantize expects a 2D CUDA tensor")
+    if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise TypeError(f"Unsupported dtype {x.dtype}; use BF16 autocast / FP32 masters")
+    if any(s == 0 for s in x.stride()):
+        x = x.contiguous()
+    if signs is None:
+        signs = get_signs(x.device)
+    if seed is None:
+        seed = _SEED
+        if sr:
+            _SEED = (_SEED + 1) & 0xFFFFFFFF
+    d, s, p = nat.quantize(x, signs, round128(x.shape[0]), round128(x.shape[1]), sr_flag() if sr else 0, rht, int(seed),
+                           given_scale=pts, seed_base=base)
+    _STATS["quant"] += 1
+    _STATS["sr_quant"] += int(sr)
+    _STATS["rht_quant"] += int(rht)
+    _STATS["reused_weight_amax"] += int(pts is not None)
+    return Packed(d, s, p, x.dtype)
+
+
+def supported(x: torch.Tensor) -> bool:
+    m, n = x.shape
+    return m > 0 and n > 0 and min(x.stride()) >= 0
+
+
+def dual(x: torch.Tensor, signs: torch.Tensor, *, sr: bool = False, clock=None, offset: Optional[int] = None):
+    """One read of x -> (packing of x without RHT, packing of x^T with sign*H16/4 along the rows of x).
+    Scales amax/2688 and 4*amax/2688; SR seeds offset and offset + 1 (plus the clock's device seed base)."""
+    global _SEED
+    if not supported(x):
+        raise ValueError("Unsupported activation pair size/strides")
+    m, n = x.shape
+    mp, np_ = round128(m), round128(n)
+    d, s = _buffers(mp, np_, x.device)
+    dt, st = _buffers(np_, mp, x.device)
+    scales = nat.amax(x)
+    q, qt = scales[1], scales[2]
+    if offset is None:
+        offset = 0
+        if sr:
+            if clock is not None:
+                offset = clock.sr_calls
+                clock.sr_calls += 2
+            else:
+                offset = _SEED
+                _SEED = (offset + 2) & 0xFFFFFFFF
+    flag = sr_flag() if sr else 0
+    nat.quantize_tile(x, signs, row=dict(packed=d, scales=s, pts=q, flags=flag, seed=offset),
+                      col=dict(packed=dt, scales=st, pts=qt, flags=flag | nat.Q_RHT, seed=offset + 1),
+                      seed_base=clock.seed if (clock is not None and sr) else None)
+    _STATS["quant"] += 2
+    _STATS["rht_quant"] += 1
+    _STATS["sr_quant"] += int(sr) * 2
+    return Packed(d, s, q, x.dtype), Packed(dt, st, qt, x.dtype)
+
+
+def pair(w: torch.Tensor, pts: torch.Tensor):
+    """Both contraction directions of a contiguous weight from one tiled read: (d, s, pts, dt, st)."""
+    m, k = w.shape
+    out = nat.quantize(w, get_signs(w.device), round128(m), round128(k), 0, False, 0, given_scale=pts, pair=True)
+    return out[0], out[1], pts, out[3], out[4]
+
+
+def single(w: torch.Tensor, pts: torch.Tensor, transpose: bool):
+    """One orientation on demand (remat): packing of w, or of w^T when transpose."""
+    src = w.t() if transpose else w
+    d, s, _ = nat.quantize(src, get_signs(w.device), round128(src.shape[0]), round128(src.shape[1]), 0, False, 0, given_scale=pts)
+    return d, s
+
+
+def weight_scale(w: torch.Tensor) -> torch.Tensor:
+    """Tensor scale of a weight that has no optimizer-cached value: max(amax, 1e-12) * (1/2688), the same expression
+    the optimizer caches after an update (optimizer_v5.py:64).  The reference uses a true division for narrow masters
+    on this path (linear6.py:40), which can differ in the last bit from the cached form; one expression everywhere
+    keeps "first step after a checkpoint load" bit-identical to "next step of the running model"."""
+    return nat.amax(w)[1]
+
+
+def matmul(a: Packed, bt: Packed, *, rows: Optional[int] = None, cols: Optional[int] = None,
+           output_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a @ bt.T on the tcgen05 block-scaled kernel with the reference's rounding chain fused into the epilogue."""
+    if a.shape[1] != bt.shape[1]:
+        raise ValueError("Packed contraction dimensions do not match")
+    rows = a.shape[0] if rows is None else rows
+    cols = bt.shape[0] if cols is None else cols
+    output_dtype = a.dtype if output_dtype is None else output_dtype
+    if output_dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("Output must be FP32 or BF16")
+    _STATS["fp4_gemm"] += 1
+    return nat.gemm(a.data, a.scale, a.pts, bt.data, bt.scale, bt.pts, rows=rows, cols=cols, out_dtype=output_dtype,
+                    bias=bias, raw_bf16=a.dtype != torch.float32)
+
+
+matmul_packed = matmul
+
+
+def raw_matmul(a: Packed, bt: Packed, rows: int, cols: int) -> torch.Tensor:
+    """BF16 accumulator image without the tensor scales: the deferred weight gradient the optimizer decodes."""
+    _STATS["fp4_gemm"] += 1
+    _STATS["deferred_wgrad"] += 1
+    return nat.gemm(a.data, a.scale, None, bt.data, bt.scale, None, rows=rows, cols=cols, out_dtype=torch.bfloat16, raw_bf16=True)
