@@ -481,7 +481,7 @@ extern "C" int nvfp4_adamw_step(void* p, int master, const void* grad, int grad_
     NVFP4_REQUIRE(!scale_out || scratch, NVFP4_ERR_ARG, "nvfp4_adamw_step: the amax reduction needs scratch");
     AdamArgs a{};
     a.p = p; a.grad = grad; a.extra = extra; a.m = m; a.v = v; a.ms = ms; a.vs = vs; a.tail = tail; a.unit = unit;
-    a.sa = sa; a.sb = sb; a.ctrl = ctrl; a.scale_out = scale_out; a.scratch = static_cast<unsigned int*>(scratch);
+    a.sa = sa; a.sb = sb; a.ctrl = ctrl; a.scale_out = scale_out; a.scratch = scratch ? reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + SCRATCH_ADAM_OFFSET) : nullptr;
     a.n = n; a.grad_cols = grad_kind == 2 ? grad_cols : 1; a.grad_stride = grad_kind == 2 ? grad_stride : 1; a.grad_kind = grad_kind;
     a.lr = lr; a.decay = decay; a.b1 = b1; a.b2 = b2; a.c1 = c1; a.c2 = c2; a.eps = eps; a.grad_mul = grad_mul;
     a.step = step; a.key = key;

@@ -23,6 +23,14 @@ int launch_status(const char* what);
         }                                     \
     } while (0)
 
+// Layout of the caller-provided scratch block (zeroed once, every kernel leaves its part zeroed again):
+//   [0, 4112)     amax partials + ticket          (quantize.cu)
+//   [4112, 4128)  the four amax results of nvfp4_quantize
+//   [4128, 4144)  AdamW: amax bits, ticket        (adamw.cu)
+constexpr int SCRATCH_AMAX_OUT_OFFSET = 4112;
+constexpr int SCRATCH_ADAM_OFFSET = 4128;
+constexpr int SCRATCH_BYTES = 4160;
+
 __host__ __device__ __forceinline__ int64_t round128(int64_t n) { return (n + 127) / 128 * 128; }
 
 // ---- element loads: every source value enters the quantiser as float(bf16_rne(x)) -------------

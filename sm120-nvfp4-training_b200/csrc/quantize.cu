@@ -447,7 +447,8 @@ using namespace nvfp4;
 
 extern "C" const char* nvfp4_last_error(void) { return g_error; }
 extern "C" int nvfp4_version(void) { return 1; }
-extern "C" int64_t nvfp4_amax_scratch_bytes(void) { return static_cast<int64_t>(sizeof(AmaxScratch)) + 16; }
+extern "C" int64_t nvfp4_amax_scratch_bytes(void) { static_assert(sizeof(AmaxScratch) == SCRATCH_AMAX_OUT_OFFSET, "scratch layout");
+    return SCRATCH_BYTES; }
 
 static bool dtype_ok(int dt) { return dt == NVFP4_F32 || dt == NVFP4_BF16 || dt == NVFP4_F16; }
 
@@ -525,7 +526,7 @@ extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, in
     const float* pts = given_scale;
     if (!given_scale) {
         // the four amax results land in the scratch tail; the scale this call needs also goes to pts_out
-        float* out4 = reinterpret_cast<float*>(static_cast<char*>(scratch) + sizeof(AmaxScratch));
+        float* out4 = reinterpret_cast<float*>(static_cast<char*>(scratch) + SCRATCH_AMAX_OUT_OFFSET);
         int rc = launch_amax(x, dtype, m, k, s0, s1, scratch, out4, pts_out, rht ? 2 : 1, stream);
         if (rc != NVFP4_OK) return rc;
         pts = pts_out;

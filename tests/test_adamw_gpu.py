@@ -148,3 +148,24 @@ def test_device_control_tensor_overrides_step_scalars(native):
                           key=4242, ctrl=ctrl)
         outs.append((p.clone(), m.clone(), v.clone()))
     assert all(torch.equal(a, b) for a, b in zip(*outs))
+
+
+def test_scale_reduction_is_independent_of_earlier_amax_calls(native):
+    """The quantiser's amax pass and the optimizer's amax reduction share one scratch block; they must not see each
+    other's leftovers."""
+    n = 65536
+    g = torch.Generator().manual_seed(3)
+    w = (torch.randn(n, generator=g) * 0.02).cuda()
+    grad = torch.randn(n, generator=g).bfloat16().cuda()
+    native.amax(torch.randn(512, 512, device="cuda").bfloat16())     # leaves partial maxima behind
+    p, _ = native.split_init(w, 17)
+    m, v, ms, vs = _state(n, "half16_v8")
+    scale = torch.full((1,), -1.0, device="cuda")
+    h = O.adam_hyper(1e-3, (0.9, 0.999), 1e-8, 0.01, 1)
+    native.adamw_step(p, 17, grad, m, v, ms, vs, vbits=8, mbits=8, nonlinear_m=False, state_block=512, hyper=h, step=1, key=9,
+                      scale_out=scale)
+    want = native.amax(p.view(1, -1))[1]
+    assert scale.item() == want.item()
+    native.adamw_step(p, 17, grad, m, v, ms, vs, vbits=8, mbits=8, nonlinear_m=False, state_block=512, hyper=h, step=2, key=9,
+                      scale_out=scale)
+    assert scale.item() == native.amax(p.view(1, -1))[1].item()
