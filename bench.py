@@ -1,6 +1,6 @@
 """Benchmark of the NVFP4 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload quant|linear|train] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload train|quant] [--impl reference]
 
 Prints ONE JSON line (rank 0).  Timing: CUDA events on the launching stream, max over ranks, inputs
 rotated through a set larger than the 126 MB L2 so no timed step finds its input cached.
@@ -237,27 +237,217 @@ def cpu_quant_baseline(base: torch.Tensor, budget_s: float = 12.0):
             "sample": f"{reps} full C1 steps (4 passes each) on the OpenMP C oracle"}
 
 
+# ------------------------------------------------------------------------------------------------
+# workload: packed NVFP4 linear layer, forward + dgrad + wgrad (config 2) -- GEMM TFLOP/s
+# ------------------------------------------------------------------------------------------------
+C2 = dict(tokens=8192, d_in=4096, d_out=4096)
+FP4_NOMINAL_TFLOPS = 9000.0
+
+
+def time_kernel(fn, reps):
+    for _ in range(3):
+        fn(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def gemm_microbench(device, tokens, d_in, d_out, reps=20):
+    """The three GEMMs of one layer on rotated operand sets; returns (ms per triple, TFLOP/s, launches)."""
+    from nvfp4_training._backend import quant
+    g = torch.Generator(device=device).manual_seed(1234)
+    sets = []
+    for _ in range(3):   # 3 operand sets x ~150 MB > L2
+        x = torch.randn((tokens, d_in), device=device, generator=g).bfloat16()
+        w = torch.randn((d_out, d_in), device=device, generator=g) * 0.02
+        gy = (torch.randn((tokens, d_out), device=device, generator=g) * 1e-3).bfloat16()
+        signs = quant.get_signs(device)
+        a, xt = quant.dual(x, signs)
+        wd, ws, wp, wtd, wts = quant.pair(w, quant.weight_scale(w))
+        ga, gt = quant.dual(gy, signs, sr=True, offset=1234)
+        sets.append((a, xt, quant.Packed(wd, ws, wp, torch.bfloat16), quant.Packed(wtd, wts, wp, torch.bfloat16), ga, gt))
+
+    def triple(i):
+        a, xt, w, wt, ga, gt = sets[i % len(sets)]
+        quant.matmul(a, w, rows=tokens, cols=d_out, output_dtype=torch.bfloat16)
+        quant.matmul(ga, wt, rows=tokens, cols=d_in, output_dtype=torch.bfloat16)
+        quant.raw_matmul(gt, xt, d_out, d_in)
+    ms = time_kernel(triple, reps)
+    flops = 3 * 2.0 * tokens * d_in * d_out
+    return ms, flops / (ms * 1e-3) / 1e12
+
+
+def quant_microbench(device, reps=30):
+    """Dual quantiser (amax + tile kernel) on rotated 4096x4096 BF16 inputs: GB/s over the single-read bytes."""
+    from nvfp4_training._backend import quant
+    xs = [c1_input(i).to(device) for i in range(8)]
+    signs = quant.get_signs(device)
+    ms = time_kernel(lambda i: quant.quantize(xs[i % 8], rht=True, signs=signs), reps)
+    return ms, C1_BYTES_PER_PASS / (ms * 1e-3) / 1e9
+
+
+# ------------------------------------------------------------------------------------------------
+# workload: full-parameter training step of the ~3.8B decoder (config 3), data parallel over the ranks
+# ------------------------------------------------------------------------------------------------
+C3 = dict(layers=32, dim=3072, heads=24, ffn=8192, vocab=32000, seq=2048, micro_batch=4)
+
+
+def run_train(args, rank, world, device):
+    import nvfp4_training as nv
+    from nvfp4_training import _native as nat
+    from nvfp4_training._workloads.llama import Decoder, linear_parameters, token_loss, warm_attention
+    cfg = dict(C3)
+    if args.layers:
+        cfg["layers"] = args.layers
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = Decoder(layers=cfg["layers"], dim=cfg["dim"], heads=cfg["heads"], ffn=cfg["ffn"], vocab=cfg["vocab"], seq=cfg["seq"])
+    model = nv.enable_nvfp4(model, profile="balanced", lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    if world > 1:
+        nv.enable_data_parallel(model)
+    n_linear = linear_parameters(model)
+    n_params = sum(p.numel() for p in model.parameters())
+    mb, seq = cfg["micro_batch"], cfg["seq"]
+    tokens = mb * seq
+    total = args.warmup + args.steps + 6
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab"], (total, world, mb, seq + 1), generator=gen)[:, rank].contiguous().pin_memory()
+    x0, y0 = ids[0, :, :-1].to(device), ids[0, :, 1:].to(device)
+    warm_attention(model, mb, seq, device)
+    torch.cuda.reset_peak_memory_stats()
+    graph = nv.capture_step(model, token_loss, x0, y0, steps=total)
+    dev_ids = ids.to(device)
+    losses = []
+    with graph:
+        step_i = 0
+        for _ in range(args.warmup):
+            graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
+        barrier(world)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(torch.cuda.current_device()) as clk:
+            ev0.record()
+            for _ in range(args.steps):
+                loss = graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
+            ev1.record()
+            barrier(world)
+        ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps, world, device)
+        losses.append(float(loss.item()))
+        # end to end: token ids come from pinned host memory, the loss goes back to the host, every step
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        xb, yb = torch.empty_like(x0), torch.empty_like(y0)
+        barrier(world)
+        e0.record()
+        for _ in range(3):
+            xb.copy_(ids[step_i, :, :-1], non_blocking=True); yb.copy_(ids[step_i, :, 1:], non_blocking=True)
+            losses.append(float(graph.step(xb, yb).item())); step_i += 1
+        e1.record()
+        barrier(world)
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / 3, world, device)
+        launches = graph.sr_calls  # SR quantiser launches per step; the full count is derived below
+    nv.check_finite(model)
+    peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
+    n_layers_linear = sum(1 for m in model.modules() if isinstance(m, torch.nn.Linear))
+    # per converted layer and step: 2 amax + 2 dual + 1 weight pair + 3 GEMM + 1 AdamW; plus one AdamW per other parameter
+    kernel_launches = n_layers_linear * 9 + (len(list(model.parameters())) - n_layers_linear)
+    pk = peaks()
+    gemm_ms, gemm_tf = gemm_microbench(device, tokens, cfg["dim"], cfg["ffn"])
+    c2_ms, c2_tf = gemm_microbench(device, C2["tokens"], C2["d_in"], C2["d_out"])
+    q_ms, q_gbs = quant_microbench(device)
+    fp4_peak = 4.0 * pk["bf16_tflops"]
+    linear_flops = 6.0 * n_linear * tokens
+    line = {
+        "metric": "nvfp4_train_tokens_per_s", "value": world * tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate); bf16 attention", "data": "synthetic",
+        "config": {"workload": f"C3: Llama-style decoder {n_params / 1e9:.2f}B params ({cfg['layers']} layers, d {cfg['dim']}, {cfg['heads']} heads, "
+                               f"SwiGLU {cfg['ffn']}, vocab {cfg['vocab']}), seq {seq}, micro-batch {mb} per GPU, balanced profile, "
+                               "compressed AdamW lr 3e-4 betas (0.9,0.95) wd 0.1, whole step replayed as one CUDA graph",
+                   "global_batch": world * mb, "seq_len": seq, "parallelism": f"dp{world}",
+                   "l2": "per-step working set (weights 7.6 GB + activations) exceeds the 126 MB L2"},
+        "tokens_per_s_per_gpu": tokens / (ms * 1e-3), "train_peak_GiB": peak_gib, "loss": losses[0],
+        "linear_tflops_in_step": linear_flops / (ms * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak, "traffic": None,
+                     "kernel": f"gemm_kernel<256> fprop+dgrad+wgrad of a {cfg['dim']}x{cfg['ffn']} layer at {tokens} tokens",
+                     "kernel_ms": gemm_ms, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)", "frac_of_nominal_9PF": gemm_tf / FP4_NOMINAL_TFLOPS},
+        "kernels": {"c2_linear_gemm_tflops": c2_tf, "c2_ms": c2_ms, "c1_quantize_GBps": q_gbs, "c1_quantize_ms": q_ms,
+                    "c1_frac_of_hbm": q_gbs / pk["hbm_gbs"]},
+        "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(xb.numel() + yb.numel()) * 8,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": kernel_launches * args.steps,
+        "clocks": clk.summary(),
+    }
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        line["cpu_baseline"] = cpu_train_baseline(cfg, budget_tokens=512)
+    return line
+
+
+def cpu_train_baseline(cfg, budget_tokens=512):
+    """The oracle on the host cores: the seven linears of ONE decoder layer (quantise, three FP32 matmuls on the decoded
+    operands, rescale) at `budget_tokens` tokens plus the compressed AdamW of that layer; extrapolated to the full token
+    count and layer count.  Attention, norms, embedding and head are not included: an optimistic CPU figure."""
+    import oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    d, f = cfg["dim"], cfg["ffn"]
+    shapes = [(d, d)] * 4 + [(d, f)] * 2 + [(f, d)]
+    g = torch.Generator().manual_seed(0)
+    tokens_full = cfg["micro_batch"] * cfg["seq"]
+    t_lin = t_adam = 0.0
+    signs = O.default_signs()
+    for k, n in shapes:
+        x = torch.randn((budget_tokens, k), generator=g).bfloat16()
+        gy = (torch.randn((budget_tokens, n), generator=g) * 1e-3).bfloat16()
+        w = (torch.randn((n, k), generator=g) * 0.02).half()
+        xb, gb, wb = (t.view(torch.int16).numpy().view(np.uint16) for t in (x, gy, w))
+        t0 = time.perf_counter()
+        row, col = O.dual(xb, signs=signs)
+        wr, wc = O.weight_pair(wb, kind="f16")
+        y = O.matmul_packed(row, wr, budget_tokens, n)
+        grow, gcol = O.dual(gb, sr_mode=O.SR_HASH, signs=signs, seed=7)
+        dx = O.matmul_packed(grow, wc, budget_tokens, k)
+        raw = O.matmul_packed(gcol, col, n, k, out_bf16=True)
+        t_lin += time.perf_counter() - t0
+        m = np.zeros(n * k, np.int8); v = np.zeros(n * k, np.uint8)
+        ms, vs = np.zeros(-(-n * k // 512), np.float32), np.zeros(-(-n * k // 512), np.float32)
+        grad = O.to_bf16_bits(raw.reshape(-1))
+        t0 = time.perf_counter()
+        O.adam_update("half16_v8", wb.reshape(-1).copy(), grad, m, v, ms, vs, step=1, key=1, hyper=O.adam_hyper(3e-4, (0.9, 0.95), 1e-8, 0.1, 1), grad_kind=1)
+        t_adam += time.perf_counter() - t0
+    layer_s = t_lin * (tokens_full / budget_tokens) + t_adam
+    step_s = layer_s * cfg["layers"]
+    return {"value": tokens_full / step_s, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"one decoder layer's 7 linears fwd+dgrad+wgrad at {budget_tokens} tokens ({t_lin:.1f} s) + its compressed AdamW "
+                      f"({t_adam:.1f} s) on the CPU oracle; extrapolated x{tokens_full // budget_tokens} tokens x{cfg['layers']} layers; "
+                      "attention / embedding / head excluded"}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return None
-    base = c1_input(0)
-    for _ in range(min(args.warmup, 1)):
-        cpu_quant_baseline(base, budget_s=1.0)
-    res = cpu_quant_baseline(base, budget_s=max(5.0, 2.0 * args.steps))
-    ms = 4 * C1_BYTES_PER_PASS / (res["value"] * 1e9) * 1e3
-    return {"impl": "reference", "metric": "nvfp4_quantize_dequantize_GBps", "value": res["value"], "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16->e2m1/ue4m3 (fp32 math)", "data": "synthetic",
-            "config": {"workload": "C1: 4096x4096 BF16; CPU restatement of the reference kernels (the reference itself needs an SM120 GPU)"},
-            "cpu_baseline": res, "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    cfg = dict(C3)
+    res = None
+    for _ in range(max(1, min(args.steps, 3))):
+        res = cpu_train_baseline(cfg, budget_tokens=256)
+    tokens = cfg["micro_batch"] * cfg["seq"]
+    return {"impl": "reference", "metric": "nvfp4_train_tokens_per_s", "value": res["value"], "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": tokens / res["value"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 arithmetic restated in FP32 on the CPU", "data": "synthetic",
+            "config": {"workload": "C3 on the host cores: CPU restatement of the reference kernels (the reference itself needs an SM120 GPU "
+                                   "and has no CPU path); extrapolated from one layer", "global_batch": cfg["micro_batch"], "seq_len": cfg["seq"]},
+            "cpu_baseline": res, "e2e": {"value": res["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="quant")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="train", choices=("train", "quant"))
+    ap.add_argument("--layers", type=int, default=0, help="override the decoder depth (smoke runs only; the metric needs the default)")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
@@ -275,7 +465,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    line = {"quant": run_quant}[args.workload](args, rank, world, device)
+    line = {"quant": run_quant, "train": run_train}[args.workload](args, rank, world, device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -74,6 +74,18 @@ class Decoder(nn.Module):
         return self.head(self.norm(x))
 
 
+def warm_attention(model, batch, seq, device):
+    """Run the attention operator once, forward and backward, with the training shapes.  Library back ends (cuDNN,
+    cuBLAS) create handles, plans and workspaces on first use, in the calling thread and in autograd's worker thread;
+    that must happen before a CUDA-graph capture."""
+    heads = model.blocks[0].heads
+    q, k, v = (torch.randn(batch, heads, seq, model.head_dim, device=device, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    F.scaled_dot_product_attention(q, k, v, is_causal=True).float().sum().backward()
+    h = torch.randn(batch * seq, 64, device=device, dtype=torch.bfloat16, requires_grad=True)
+    F.cross_entropy((h @ h.t()[:, :128]).float(), torch.zeros(batch * seq, dtype=torch.long, device=device)).backward()
+    torch.cuda.synchronize(device)
+
+
 def token_loss(model, ids, targets):
     logits = model(ids)
     return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.view(-1))
