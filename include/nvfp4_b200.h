@@ -92,6 +92,25 @@ int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, i
                    uint8_t* packed_t, uint8_t* scales_t, void* scratch, nvfp4_stream_t stream);
 
 /*
+ * nvfp4_quantize for callers that cannot allocate device memory.  No counterpart in the reference project.
+ * Some hosts of this library own no allocator they may call at this point: a plug-in running inside another
+ * framework's execution callback, a replayed step whose memory plan is frozen, a process whose device memory was handed
+ * out up front.  nvfp4_quantize asks such callers for a scratch block they cannot provide; this variant keeps the block
+ * (the amax partial maxima, the arrival ticket and the four scale results: 4160 bytes) in a __device__ array inside
+ * the library image instead, so every GPU that loads the library holds those 4160 bytes until the process exits.
+ * Same arguments and results as nvfp4_quantize without given_scale / pair / scratch; the tensor scale is always
+ * computed and written to pts_out.  Tensors above nvfp4_quantize_static_max_elements() (2^31) elements are refused with
+ * NVFP4_ERR_ARG.  The call performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls on a device share the one array: calls that
+ * may overlap on the GPU (different streams, no ordering) race on it and must be serialised by the caller.
+ */
+int64_t nvfp4_quantize_static_max_elements(void);
+int nvfp4_quantize_static(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,
+                          int sr, int rht, uint32_t seed, const float* signs, const int32_t* seed_base, uint8_t* packed,
+                          uint8_t* scales, float* pts_out, nvfp4_stream_t stream);
+
+/*
  * NVFP4 -> FP32 or BF16: out[r][c] = (level * block_scale) * pts for r < rows, c < cols.
  * Replaces dequant (src/precision_lora/_packed_cuda.py:56-63) and the TorchAO NVFP4Tensor.dequantize used
  * by the reference's verifier (src/nvfp4_training/_verification/nvfp4_cuda.py:184-200).

@@ -11,6 +11,7 @@
 
 #include <cstdarg>
 #include <cstring>
+#include <cstddef>
 #include <algorithm>
 
 namespace nvfp4 {
@@ -562,4 +563,44 @@ extern "C" int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, co
     if (out_dtype == NVFP4_BF16) dequant_kernel<true><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride, vec_ok);
     else dequant_kernel<false><<<blocks, 256, 0, st>>>(packed, scales, pts, kp, rows, cols, hi_first, out, out_stride, vec_ok);
     return launch_status("nvfp4_dequantize");
+}
+
+// ================================================================================================
+// Entry point for callers that cannot allocate device memory
+// ================================================================================================
+namespace nvfp4 {
+// Scratch of the amax stage for nvfp4_quantize_static: lives in the library image, one copy per GPU that loads it.
+static __device__ __align__(256) unsigned char g_static_scratch[SCRATCH_BYTES];
+constexpr int64_t STATIC_MAX_ELEMENTS = int64_t(1) << 31;
+constexpr int MAX_DEVICES = 64;
+static void* g_static_scratch_addr[MAX_DEVICES] = {};
+}  // namespace nvfp4
+
+extern "C" int64_t nvfp4_quantize_static_max_elements(void) { return STATIC_MAX_ELEMENTS; }
+
+extern "C" int nvfp4_quantize_static(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp,
+                                     int64_t kp, int sr, int rht, uint32_t seed, const float* signs, const int32_t* seed_base,
+                                     uint8_t* packed, uint8_t* scales, float* pts_out, nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(x && packed && scales && signs && pts_out, NVFP4_ERR_ARG, "nvfp4_quantize_static: null pointer");
+    NVFP4_REQUIRE(m > 0 && k > 0, NVFP4_ERR_ARG, "nvfp4_quantize_static: empty tensor");
+    NVFP4_REQUIRE(m <= STATIC_MAX_ELEMENTS / k, NVFP4_ERR_ARG,
+                  "nvfp4_quantize_static: %lld x %lld elements exceed the limit of %lld of the built-in scratch variant; "
+                  "use nvfp4_quantize with caller-provided scratch", (long long)m, (long long)k, (long long)STATIC_MAX_ELEMENTS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    NVFP4_REQUIRE(e == cudaSuccess && dev >= 0 && dev < MAX_DEVICES, NVFP4_ERR_LAUNCH, "nvfp4_quantize_static: no usable current device");
+    if (!g_static_scratch_addr[dev]) {
+        // The symbol name is only a host-side handle; the kernel needs the address the array has on THIS device.
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        NVFP4_REQUIRE(e == cudaSuccess && addr, NVFP4_ERR_LAUNCH, "nvfp4_quantize_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_static_scratch_addr[dev] = addr;
+    }
+    void* scratch = g_static_scratch_addr[dev];
+    // Every call shares the array and it keeps what the last call left: the arrival ticket must start at zero.
+    e = cudaMemsetAsync(static_cast<char*>(scratch) + offsetof(AmaxScratch, ticket), 0, sizeof(unsigned int),
+                        reinterpret_cast<cudaStream_t>(stream));
+    NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_quantize_static: cannot clear the ticket: %s", cudaGetErrorString(e));
+    return nvfp4_quantize(x, dtype, m, k, s0, s1, mp, kp, sr, rht, seed, signs, nullptr, seed_base, 0, packed, scales, pts_out,
+                          nullptr, nullptr, scratch, stream);
 }

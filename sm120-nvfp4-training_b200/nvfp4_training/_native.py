@@ -29,6 +29,8 @@ _SIGNATURES = {
     "nvfp4_amax": (I32, [P, I32, I64, I64, I64, I64, P, P, P]),
     "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P]),
     "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P]),
+    "nvfp4_quantize_static_max_elements": (I64, []),
+    "nvfp4_quantize_static": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, P, P, P]),
     "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
     "nvfp4_adamw_step": (I32, [P, I32, P, I32, I64, I64, P, P, P, F, P, P, P, P, P, P, I64, I32, I32, I32, I32,
                                  F, F, F, F, F, F, F, U32, U32, P, P, P, P]),
