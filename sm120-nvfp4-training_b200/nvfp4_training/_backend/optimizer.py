@@ -180,6 +180,16 @@ class AdamW(torch.optim.Optimizer):
             for p, g in active:
                 self._update_param(p, g, pending.pop(p, None))
 
+    def _finish_streamed(self, p, group, pack, held):
+        """Update p from a gradient whose all-reduce has completed (stream-wise)."""
+        grad = held.pop(p, None)
+        if pack is not None and pack[1] is None and pack[2] is None and grad is not None and pack[0] is grad:
+            p.grad = grad                     # dense leaf gradient: the ordinary path reads p.grad
+            self._update_param(p, group, None)
+            p.grad = None
+        else:
+            self._update_param(p, group, pack)
+
     def capture_streaming_backward(self, loss):
         """Record parameter-local updates once, as soon as each parameter's gradient is complete, inside backward
         (peak memory = one layer's gradient).  Only valid while a CUDA graph is being captured."""
@@ -191,7 +201,7 @@ class AdamW(torch.optim.Optimizer):
             raise ValueError("Distinct optimizer entries may not alias storage")
         if any(p.grad is not None or p._backward_hooks or p._post_accumulate_grad_hooks for p, g in params):
             raise ValueError("Clear gradients and remove gradient hooks before capture")
-        pending, completed, handles = {}, set(), []
+        pending, completed, handles, held = {}, set(), [], {}
         owners = self._owners(params)
         reducer = self.reducer
 
@@ -201,10 +211,14 @@ class AdamW(torch.optim.Optimizer):
                 if p in completed or (pack is None and p.grad is None):
                     raise RuntimeError("Unexpected leaf gradient during capture")
                 with torch.no_grad():
-                    if reducer is not None:
-                        reducer.capture_reduce(p, pack)
-                    self._update_param(p, group, pack)
-                p.grad = None
+                    if reducer is None:
+                        self._update_param(p, group, pack)
+                        p.grad = None
+                    else:
+                        held[p] = p.grad          # keep the leaf gradient alive until its collective is consumed
+                        p.grad = None
+                        for q, gq, packq in reducer.submit(p, group, pack if pack is not None else (held[p], None, None)):
+                            self._finish_streamed(q, gq, packq, held)
                 completed.add(p)
             return update
         try:
@@ -218,6 +232,10 @@ class AdamW(torch.optim.Optimizer):
                 node = torch.autograd.graph.get_gradient_edge(p).node
                 handles.append(node.register_hook(ready(p, group)))
             loss.backward()
+            if reducer is not None:
+                with torch.no_grad():
+                    for q, gq, packq in reducer.drain():
+                        self._finish_streamed(q, gq, packq, held)
             if pending or len(completed) != len(params):
                 raise RuntimeError("Every parameter must receive its complete gradient once")
         finally:

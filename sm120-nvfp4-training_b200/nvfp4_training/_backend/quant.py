@@ -16,6 +16,7 @@ from .. import _native as nat
 
 _SIGNS: dict = {}
 _SEED = 0
+_RANK_OFFSET = 0   # added to stochastic-rounding seeds; set per rank by nvfp4_training.distributed
 _STATS = {"fp4_gemm": 0, "quant": 0, "sr_quant": 0, "rht_quant": 0, "reused_weight_amax": 0,
           "packed_activation_saved": 0, "deferred_wgrad": 0, "optimizer_scale_hits": 0, "v5_pair": 0}
 
@@ -92,6 +93,8 @@ def quantize(x: torch.Tensor, *, sr: bool = False, rht: bool = False, signs: Opt
         seed = _SEED
         if sr:
             _SEED = (_SEED + 1) & 0xFFFFFFFF
+    if sr:
+        seed = int(seed) + _RANK_OFFSET
     d, s, p = nat.quantize(x, signs, round128(x.shape[0]), round128(x.shape[1]), sr_flag() if sr else 0, rht, int(seed),
                            given_scale=pts, seed_base=base)
     _STATS["quant"] += 1
@@ -128,6 +131,8 @@ def dual(x: torch.Tensor, signs: torch.Tensor, *, sr: bool = False, clock=None, 
                 offset = _SEED
                 _SEED = (offset + 2) & 0xFFFFFFFF
     flag = sr_flag() if sr else 0
+    if sr:
+        offset = offset + _RANK_OFFSET
     nat.quantize_tile(x, signs, row=dict(packed=d, scales=s, pts=q, flags=flag, seed=offset),
                       col=dict(packed=dt, scales=st, pts=qt, flags=flag | nat.Q_RHT, seed=offset + 1),
                       seed_base=clock.seed if (clock is not None and sr) else None)

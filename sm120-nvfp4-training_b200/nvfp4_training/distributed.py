@@ -1,0 +1,119 @@
+"""Data-parallel training: replicas that all-reduce weight gradients over NCCL (NVLink / NVSwitch).
+
+The reference is single-GPU; this module is new.  Design:
+  * every converted layer owns a persistent flat BF16 gradient slot; the wgrad GEMM's epilogue writes the scaled
+    gradient straight into it (no pack / copy kernel between GEMM and collective);
+  * a slot is all-reduced asynchronously as soon as its layer's backward has produced it, in backward order, so the
+    transfer overlaps the remaining backward compute (NCCL runs on its own stream; only the consumer waits);
+  * the fused AdamW kernel reads the reduced slot in place and folds the 1/world_size into its gradient decode;
+  * gradients that autograd leaves in .grad (norm gains, biases, embeddings) are reduced the same way in FP32;
+  * stochastic-rounding seeds of gradient quantisation get a per-rank offset; weights are re-quantised locally and are
+    identical on all ranks because weights, rounding keys and step numbers are.
+Works eagerly and under CUDA-graph capture (the update of a parameter is deferred by `depth` parameters so that its
+collective has time to finish).  Plain loads / NCCL only: no peer-memory kernels, no TMA multicast.
+"""
+from __future__ import annotations
+
+from collections import deque
+
+import torch
+import torch.distributed as dist
+
+
+class GradientReducer:
+    def __init__(self, params, process_group=None, *, slot_dtype=torch.bfloat16, depth=2, owner_filter=None):
+        self.group = process_group
+        self.world = dist.get_world_size(process_group)
+        self.rank = dist.get_rank(process_group)
+        self.grad_scale = 1.0 / self.world
+        self.depth = max(0, int(depth))
+        self.slot_dtype = slot_dtype
+        self._slots = {}
+        owners = [p for p in params if (owner_filter(p) if owner_filter else getattr(p, "_v4_request_scale", False))]
+        for p in owners:
+            self._slots[p] = torch.zeros(p.numel(), dtype=slot_dtype, device=p.device)
+        self._works = []          # eager mode: outstanding collectives
+        self._queue = deque()     # capture / streaming mode: (param, group, pack, work) waiting for their collective
+        self.launched = []        # order in which slots were reduced (introspection / tests)
+
+    # ---- used by the linear layer's backward ------------------------------------------------------------
+    def has_slot(self, p) -> bool:
+        return p in self._slots
+
+    def slot(self, p) -> torch.Tensor:
+        return self._slots[p]
+
+    def ready(self, p):
+        """The slot of p holds this rank's gradient: start its all-reduce (eager mode)."""
+        if self._streaming:
+            return
+        self._works.append(dist.all_reduce(self._slots[p], group=self.group, async_op=True))
+        self.launched.append(p)
+
+    # ---- eager protocol (backward_step / step) ----------------------------------------------------------
+    def begin(self, params, capturing=False):
+        self._streaming = bool(capturing)
+        self._works.clear()
+        self._queue.clear()
+        self.launched.clear()
+
+    def finish(self, dense_params):
+        """Reduce the gradients autograd left in .grad, then wait (stream-wise) for every collective."""
+        self.reduce_dense(dense_params)
+        for work in self._works:
+            work.wait()
+        self._works.clear()
+
+    def reduce_dense(self, params):
+        for p in params:
+            if p.grad is not None:
+                self._works.append(dist.all_reduce(p.grad, group=self.group, async_op=True))
+        if not getattr(self, "_streaming", False):
+            for work in self._works:
+                work.wait()
+            self._works.clear()
+
+    # ---- streaming protocol (updates inside backward, eager or captured) ------------------------------
+    def submit(self, p, group, pack):
+        """Start the collective for p's gradient and return the (param, group, pack) items whose collectives have had
+        `depth` later submissions to overlap with; those are safe to update now (after a stream-level wait)."""
+        tensor = pack[0] if pack is not None else p.grad
+        work = dist.all_reduce(tensor, group=self.group, async_op=True)
+        self.launched.append(p)
+        self._queue.append((p, group, pack, work))
+        ready = []
+        while len(self._queue) > self.depth:
+            q, g, k, w = self._queue.popleft()
+            w.wait()
+            ready.append((q, g, k))
+        return ready
+
+    def drain(self):
+        ready = []
+        while self._queue:
+            q, g, k, w = self._queue.popleft()
+            w.wait()
+            ready.append((q, g, k))
+        return ready
+
+
+def enable_data_parallel(model, process_group=None, *, bucket_mb=None, depth=2):
+    """Attach a GradientReducer to model.nvfp4_optimizer.  Call after enable_nvfp4 on every rank with identical
+    initial weights (same seed); the process group defaults to the world group."""
+    if not dist.is_initialized():
+        raise RuntimeError("torch.distributed must be initialised before enable_data_parallel")
+    opt = model.nvfp4_optimizer
+    params = [p for g in opt.param_groups for p in g["params"]]
+    reducer = GradientReducer(params, process_group, depth=depth)
+    opt.reducer = reducer
+    from ._backend import quant
+    quant._RANK_OFFSET = (reducer.rank * 0x9E3779B1) & 0xFFFFFFFF
+    # replicas must start from identical weights
+    with torch.no_grad():
+        for p in params:
+            src = p.view(torch.uint8) if p.dtype == torch.float8_e4m3fn else p
+            dist.broadcast(src, src=dist.get_global_rank(process_group, 0) if process_group is not None else 0, group=process_group)
+        for b in model.buffers():
+            if b.is_floating_point() or b.dtype in (torch.uint8, torch.int8):
+                dist.broadcast(b, src=dist.get_global_rank(process_group, 0) if process_group is not None else 0, group=process_group)
+    return model

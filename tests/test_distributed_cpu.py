@@ -1,0 +1,76 @@
+"""Host-side logic of the data-parallel gradient reducer, on two CPU ranks over gloo."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import sys
+        from pathlib import Path
+        sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "sm120-nvfp4-training_b200"))
+        from nvfp4_training.distributed import GradientReducer
+        torch.manual_seed(0)
+        params = [torch.nn.Parameter(torch.zeros(8 + i)) for i in range(5)]
+        for p in params[:3]:
+            p._v4_request_scale = True       # "converted layer weights": gradients live in reducer slots
+        index = {id(p): i for i, p in enumerate(params)}
+        red = GradientReducer(params, slot_dtype=torch.float32, depth=2)
+        assert red.world == world and red.grad_scale == 1.0 / world
+        assert [red.has_slot(p) for p in params] == [True, True, True, False, False]
+
+        # ---- streaming protocol: updates lag the submissions by `depth` --------------------------------
+        red.begin(params, capturing=True)
+        order, updated = [], []
+        for i, p in reversed(list(enumerate(params))):          # backward order
+            if red.has_slot(p):
+                red.slot(p).fill_(float(rank + 1) * (i + 1))
+                pack = (red.slot(p), None, None)
+            else:
+                p.grad = torch.full_like(p, float(rank + 1) * (i + 1))
+                pack = (p.grad, None, None)
+            ready = red.submit(p, "group", pack)
+            order.append(i)
+            assert len(red._queue) <= 2
+            updated += [(index[id(q)], float(k[0][0])) for q, _, k in ready]
+        updated += [(index[id(q)], float(k[0][0])) for q, _, k in red.drain()]
+        assert [i for i, _ in updated] == order == [4, 3, 2, 1, 0]
+        total = sum(r + 1 for r in range(world))
+        assert all(abs(v - total * (i + 1)) < 1e-6 for i, v in updated)
+
+        # ---- eager protocol: slots reduced when ready, dense gradients in finish() ---------------------
+        red.begin(params)
+        for i in (2, 1, 0):
+            red.slot(params[i]).fill_(float(rank))
+            red.ready(params[i])
+        for p in params[3:]:
+            p.grad = torch.full_like(p, 10.0 + rank)
+        red.finish(params[3:])
+        assert all(float(red.slot(p)[0]) == sum(range(world)) for p in params[:3])
+        assert all(float(p.grad[0]) == sum(10.0 + r for r in range(world)) for p in params[3:])
+        assert [index[id(p)] for p in red.launched] == [2, 1, 0]
+        results[rank] = "ok"
+    except Exception as e:  # pragma: no cover - reported to the parent
+        results[rank] = repr(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reducer_protocols_on_two_gloo_ranks():
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}
