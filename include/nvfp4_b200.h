@@ -174,6 +174,18 @@ int nvfp4_adamw_plain(float* p, const float* grad, float* m, float* v, int64_t n
  */
 int nvfp4_split_init(const float* src, int64_t n, int master, void* hi, int8_t* tail, nvfp4_stream_t stream);
 
+/*
+ * Workload helpers (BF16, element-wise, fused): rotary position embedding on [tokens][heads][dim] rows (split-half
+ * convention, tables cos/sin [seq][dim/2], inverse != 0 applies the transpose rotation = the backward pass), and SwiGLU
+ * gating out = silu(gate) * up (dout == NULL) or its backward (dgate -> out_or_dgate, dup).  The reference keeps a rotary
+ * kernel for one of its model integrations (src/precision_lora/_packed_cuda.py:104-114) and otherwise leaves these
+ * operations to PyTorch; they are here because they sit between the NVFP4 layers of the benchmarked decoder.
+ */
+int nvfp4_rope(const void* x, void* out, const void* cos_t, const void* sin_t, int64_t tokens, int seq, int heads, int dim,
+               int64_t pitch, int inverse, nvfp4_stream_t stream);
+int nvfp4_swiglu(const void* gate, const void* up, const void* dout, void* out_or_dgate, void* dup, int64_t n,
+                 nvfp4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,10 +54,17 @@ __device__ __forceinline__ float load_abs(const void* p, int64_t i) {
 template <int DT> struct ElemSize { static constexpr int value = (DT == NVFP4_F32) ? 4 : 2; };
 
 // ---- random sources -------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t hash32(uint32_t seed, uint32_t index) {
-    uint32_t z = seed * 0x9e3779b9u + index + 0x85ebca6bu;
-    z ^= z >> 16; z *= 0x7feb352du; z ^= z >> 15; z *= 0x846ca68bu; z ^= z >> 16;
+__device__ __forceinline__ uint32_t shr_mul(uint32_t z, uint32_t pow2) {   // z >> k as the high half of z * 2^(32-k)
+    uint32_t r;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(z), "r"(pow2));
+    return r;
+}
+__device__ __forceinline__ uint32_t hash32_mixed(uint32_t z) {   // finaliser of hash32 on a pre-added input
+    z ^= shr_mul(z, 1u << 16); z *= 0x7feb352du; z ^= shr_mul(z, 1u << 17); z *= 0x846ca68bu; z ^= shr_mul(z, 1u << 16);
     return z;
+}
+__device__ __forceinline__ uint32_t hash32(uint32_t seed, uint32_t index) {
+    return hash32_mixed(seed * 0x9e3779b9u + index + 0x85ebca6bu);
 }
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
@@ -79,17 +86,21 @@ __device__ __forceinline__ float uniform24(uint32_t bits) {
 }
 
 // ---- E2M1 stochastic level choice ---------------------------------------------------------------
-__device__ __forceinline__ uint32_t sr_magnitude(float x, float u) {
-    // x in [0, 6].  Level spacing is 1/2 below 2, 1 below 4, 2 above; t counts whole steps from zero of
-    // that spacing, lo = t * spacing is the level at or below x.  (x - lo) / spacing is written as a product:
-    // the spacing is a power of two, so both forms round to the same float.  x == 6 gives lo = 4, p = 1 > u.
-    const bool s2 = x < 2.f, s4 = x < 4.f;
-    const float rw = s2 ? 2.f : (s4 ? 1.f : .5f);
-    const float w = s2 ? .5f : (s4 ? 1.f : 2.f);
-    const float t = s4 ? floorf(__fmul_rn(x, rw)) : 2.f;
-    const float lo = __fmul_rn(t, w);
-    const uint32_t code = static_cast<uint32_t>(t) + (s2 ? 0u : (s4 ? 2u : 4u));
-    return code + static_cast<uint32_t>(u < __fmul_rn(__fsub_rn(x, lo), rw));
+// x in [0, 6], h24 = 24 random bits (u = h24 * 2^-24).  Level spacing is 1/2 below 2, 1 below 4, 2 above, i.e.
+// 2^(e-1) with e the exponent of max(x, 1).  With xs = x / spacing (exact), the lower level is floor(xs) steps from
+// zero and the round-up probability is frac(xs); "u < p" is tested as "h24 < p * 2^24".  Everything is exact
+// arithmetic on the same real numbers as (x - lo) / (hi - lo) < u, so the result is bit-identical, and no
+// conversion instruction is needed: floor comes from a round-down add of 2^23, float(h24) from mantissa injection.
+__device__ __forceinline__ uint32_t sr_code(float x, uint32_t h24) {
+    const uint32_t e_biased = __float_as_uint(fmaxf(x, 1.0f)) >> 23;              // 127, 128 or 129
+    const float rw = __uint_as_float((255u - e_biased) << 23);                    // 2, 1 or 1/2
+    const float xs = __fmul_rn(x, rw);
+    const float tm = __fadd_rd(xs, 8388608.f);                                    // 2^23 + floor(xs)
+    const uint32_t steps = __float_as_uint(tm) & 7u;
+    const float p24 = __fmul_rn(__fsub_rn(xs, __fsub_rn(tm, 8388608.f)), 16777216.f);
+    const float hf = __fadd_rn(__fsub_rn(__uint_as_float(0x4B000000u | (h24 & 0x7FFFFFu)), 8388608.f),
+                               __uint_as_float((h24 >> 23) * 0x4B000000u));
+    return steps + 2u * (e_biased - 127u) + static_cast<uint32_t>(hf < p24);
 }
 
 // ---- scale-factor swizzle (32 x 4 x 4 atom inside 128-row x 4-group blocks) ------------------------

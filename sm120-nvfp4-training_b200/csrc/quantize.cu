@@ -205,13 +205,17 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
                 rnd[4 * j] = r.x; rnd[4 * j + 1] = r.y; rnd[4 * j + 2] = r.z; rnd[4 * j + 3] = r.w;
             }
         }
+        const uint32_t hbase = seed * 0x9e3779b9u + static_cast<uint32_t>(idx0) + 0x85ebca6bu;
 #pragma unroll
         for (int l = 0; l < 16; ++l) {
             const float q = __fmul_rn(v[l], mul);
-            float u;
-            if constexpr (SR == SR_HASH) u = uniform24(hash32(seed, static_cast<uint32_t>(idx0) + l));
-            else u = static_cast<float>((rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) * (1.0f / 65536.0f);
-            codes[l] = sr_magnitude(fminf(fabsf(q), 6.f), u) | ((q < 0.f) ? 8u : 0u);
+            uint32_t h24;
+            if constexpr (SR == SR_HASH) h24 = shr_mul(hash32_mixed(hbase + l), 1u << 24);
+            else h24 = ((rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8;   // 16-bit uniform on the 24-bit grid
+            // sign bit set iff q < 0 (so -0 encodes as +0): q < 0  <=>  sign bit set and magnitude non-zero
+            const uint32_t qb = __float_as_uint(q);
+            const uint32_t neg = (qb > 0x80000000u) ? 8u : 0u;
+            codes[l] = sr_code(fminf(fabsf(q), 6.f), h24) | neg;
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -338,22 +342,29 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict_
         }
     }
     if constexpr (COL) {
-        // ---- phase B: thread (n, g) encodes source rows g*16..g*16+15 of source column n ------------
+        // ---- phase B: a thread takes two adjacent source columns (one 32-bit shared load per source row) and
+        //      encodes source rows g*16 .. g*16+15 of each ----
         const float inv_c = __fdiv_rn(1.f, __ldg(C.pts));
-        const int n = tid & 127;
+        const int cp = tid & 63;
+        const bool c_rht = C.flags & NVFP4_Q_RHT, c_hi = C.flags & NVFP4_Q_HI_FIRST;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int g = (tid >> 7) + 2 * i;
-            float v[16];
+        for (int i = 0; i < 2; ++i) {
+            const int g = (tid >> 6) + 4 * i;
+            uint32_t w[16];
 #pragma unroll
-            for (int l = 0; l < 16; ++l) v[l] = bf16_value(tile[(g * 16 + l) * TILE_PITCH + n]);
-            const bool rht = C.flags & NVFP4_Q_RHT;
-            if (rht) hadamard16_unscaled(v, sg);
-            uint32_t sb;
-            uint2 p = encode16<SR>(v, rht, inv_c, C.flags & NVFP4_Q_HI_FIRST, C.seed + base,
-                                   static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16), sb);
-            *reinterpret_cast<uint2*>(col_out + n * COL_OUT_PITCH + g * 8) = p;
-            col_sc[(g >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (g & 3)] = static_cast<uint8_t>(sb);
+            for (int l = 0; l < 16; ++l) w[l] = *reinterpret_cast<const uint32_t*>(&tile[(g * 16 + l) * TILE_PITCH + 2 * cp]);
+#pragma unroll
+            for (int side = 0; side < 2; ++side) {
+                const int n = 2 * cp + side;
+                float v[16];
+#pragma unroll
+                for (int l = 0; l < 16; ++l) v[l] = __uint_as_float(side ? (w[l] & 0xffff0000u) : (w[l] << 16));
+                if (c_rht) hadamard16_unscaled(v, sg);
+                uint32_t sb;
+                uint2 p = encode16<SR>(v, c_rht, inv_c, c_hi, C.seed + base, static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16), sb);
+                *reinterpret_cast<uint2*>(col_out + n * COL_OUT_PITCH + g * 8) = p;
+                col_sc[(g >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (g & 3)] = static_cast<uint8_t>(sb);
+            }
         }
         __syncthreads();
         if (tid < 64) {

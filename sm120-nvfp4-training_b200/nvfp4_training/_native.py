@@ -36,6 +36,8 @@ _SIGNATURES = {
                                  F, F, F, F, F, F, F, U32, U32, P, P, P, P]),
     "nvfp4_adamw_plain": (I32, [P, P, P, P, I64, F, F, F, F, F, F, F, F, P, P]),
     "nvfp4_split_init": (I32, [P, I64, I32, P, P, P]),
+    "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I32, P]),
+    "nvfp4_swiglu": (I32, [P, P, P, P, P, I64, P]),
     "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
 }
 

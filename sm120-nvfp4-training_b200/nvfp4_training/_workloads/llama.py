@@ -42,12 +42,17 @@ class Block(nn.Module):
     def forward(self, x, cos, sin):
         b, s, d = x.shape
         h = self.norm1(x)
-        q, k, v = (f(h).view(b, s, self.heads, d // self.heads).transpose(1, 2) for f in (self.q, self.k, self.v))
-        q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
-        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, s, d)
-        x = x + self.o(a)
+        q, k, v = (f(h).view(b, s, self.heads, d // self.heads) for f in (self.q, self.k, self.v))
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            from .fused import rope, swiglu
+            q, k = rope(q, cos[:s], sin[:s]), rope(k, cos[:s], sin[:s])
+        else:
+            swiglu = lambda g, u: F.silu(g) * u
+            q, k = (apply_rotary(t.transpose(1, 2), cos, sin).transpose(1, 2) for t in (q, k))
+        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        x = x + self.o(a.transpose(1, 2).reshape(b, s, d))
         h = self.norm2(x)
-        return x + self.down(F.silu(self.gate(h)) * self.up(h))
+        return x + self.down(swiglu(self.gate(h), self.up(h)))
 
 
 class Decoder(nn.Module):
@@ -67,7 +72,7 @@ class Decoder(nn.Module):
         s = ids.shape[1]
         if self._tables is None or self._tables[0].shape[0] < s or self._tables[0].device != ids.device:
             self._tables = rotary_tables(max(s, self.seq), self.head_dim, ids.device)
-        cos, sin = (t[:s] for t in self._tables)
+        cos, sin = (t[:s].contiguous() for t in self._tables)
         x = self.embed(ids).to(torch.bfloat16)
         for block in self.blocks:
             x = block(x, cos, sin)
