@@ -4,7 +4,7 @@
 //   A: e2m1 payload [M][K/2] (K-major), SFA: ue4m3, one per 16 elements, in 128-row x 4-scale blocks of
 //      512 bytes ordered [M/128][K/64]; B, SFB likewise with N rows.  M, N, K are multiples of 128.
 //
-// One persistent CTA per SM, 320 threads, warp-specialised:
+// One persistent CTA per SM, 448 threads, warp-specialised:
 //   warp 0    TMA producer.  Per k-tile of 256 elements: A box 128 rows x 128 B and B box BN rows x 128 B (128-byte
 //             swizzle) plus the scale blocks as plain bulk copies, all completing on the stage's mbarrier.  Plain
 //             loads only: every CTA fetches its own tiles.
@@ -13,9 +13,11 @@
 //   warps 2-5 scale-factor movers: read the stage's scale blocks from shared memory and write them into the TMEM
 //             scale buffers with tcgen05.st (each warp fills the 32 lanes of its own sub-partition, which is the
 //             four-fold replication the MMA expects).  This keeps scale traffic out of the MMA issue pipe.
-//   warps 6-9 epilogue: tcgen05.ld -> scale / cast -> swizzled shared staging -> TMA store (which also crops).
-//             With BN = 256 the single accumulator is handed back in two halves so the next tile's first MMAs
-//             start while the second half is still being drained.
+//   warps 6-13 epilogue, two per TMEM sub-partition, each owning half of the tile's columns.  For BF16 output a warp
+//             first drains its whole share: tcgen05.ld -> bf16(acc) -> x bf16(alpha), kept as packed BF16 pairs in
+//             registers; it then hands its half of the accumulator back to the MMA warp and only afterwards pushes the
+//             registers through a small swizzled staging buffer into TMA stores (which also crop).  The next tile's
+//             MMAs therefore wait for a drain of a few hundred cycles, not for the stores.
 // Every wait is bounded: on expiry the kernel raises the status word, all roles leave their loops, the producer
 // waits (bounded) for loads still in flight, TMEM is freed and the kernel returns.
 #include "common.cuh"
@@ -26,12 +28,13 @@
 
 namespace nvfp4 {
 
-constexpr int GEMM_THREADS = 320;
+constexpr int GEMM_THREADS = 448;
 constexpr int BM = 128;
 constexpr int BK = 256;             // elements per k-tile = 128 payload bytes per row
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int SF_BLOCK = 512;       // 128 rows x 4 scales
-constexpr int EPI_SLAB_BYTES = 2048;  // 32 rows x 64 bytes per epilogue warp and buffer
+constexpr int EPI_SLAB_BYTES = 1024;  // 32 rows x 32 bytes per epilogue warp
+constexpr int EPI_WARPS = 8;
 constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
 template <int BN> struct GemmCfg {
@@ -49,8 +52,7 @@ template <int BN> struct GemmCfg {
     static constexpr int SF_BASE = ACC_COLS;
     static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int EPI_BUFS = 1;              // staging slabs per epilogue warp
-    static constexpr int EPI_BYTES = 4 * EPI_BUFS * EPI_SLAB_BYTES;
+    static constexpr int EPI_BYTES = EPI_WARPS * EPI_SLAB_BYTES;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * SF_BUFS + ACC_STAGES + ACC_STAGES * HALVES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
     static_assert(ACC_COLS + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
@@ -184,7 +186,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
         for (int s = 0; s < Cfg::SF_BUFS; ++s) { mbar_init(&sf_full[s], 4); mbar_init(&sf_empty[s], 1); }
         for (int a = 0; a < Cfg::ACC_STAGES; ++a) mbar_init(&acc_full[a], 1);
-        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], 4);
+        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], EPI_WARPS / Cfg::HALVES);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -328,9 +330,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+        const int sub = warp & 3;                    // TMEM sub-partition this warp may read
+        const int half = (warp - 6) >> 2;            // which half of the tile's columns this warp drains
+        constexpr int SHARE = BN / 2;                // columns per warp
+        constexpr int CHUNKS = SHARE / 32;           // tcgen05.ld.x32 loads per share
         const int row_in_tile = sub * 32 + lane;
-        uint8_t* slab = epi_smem + (warp - 6) * Cfg::EPI_BUFS * EPI_SLAB_BYTES;
+        uint8_t* slab = epi_smem + (warp - 6) * EPI_SLAB_BYTES;
         float alpha = 1.f;
         const bool scaled = g.pts_a != nullptr;
         if (scaled) {
@@ -338,10 +343,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (g.raw_bf16) alpha = bf16_value(bf16_bits(alpha));
         }
         const __nv_bfloat162 alpha2 = __float2bfloat162_rn(alpha);
-        const int cols_per_slab = g.out_f32 ? 16 : 32;
-        const int nslab = BN / cols_per_slab;
-        int local = 0, buf = 0;
+        const bool fast = !g.bias && g.raw_bf16 && !g.out_f32;   // BF16 chain without bias: drain first, store later
+        const int acc_slot_of_half = (Cfg::HALVES == 2) ? half : 0;
+        int local = 0;
         bool ok = true;
+
+        // writes 32 rows x 32 bytes held as two uint4 per lane: through the staging slab and a TMA store, or directly
+        auto emit = [&](const uint4& q0, const uint4& q1, int64_t row, int64_t col0, int tile_row0, int cols_here) {
+            if (g.tma_store) {
+                if (lane == 0) bulk_wait_read<0>();      // the store that last read the slab has drained it
+                __syncwarp();
+                const int sw = (lane >> 2) & 1;            // 32-byte swizzle: 16-byte chunk index ^ bit 2 of the row
+                *reinterpret_cast<uint4*>(slab + lane * 32 + ((0 ^ sw) << 4)) = q0;
+                *reinterpret_cast<uint4*>(slab + lane * 32 + ((1 ^ sw) << 4)) = q1;
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0) { tma_store_2d(&map_out, static_cast<int>(col0), tile_row0, slab); bulk_commit(); }
+            } else if (row < g.rows) {
+                const int esz = g.out_f32 ? 4 : 2;
+                uint8_t* dst = static_cast<uint8_t*>(g.out) + (row * g.ldo + col0) * esz;
+                if (col0 + cols_here <= g.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    reinterpret_cast<uint4*>(dst)[0] = q0; reinterpret_cast<uint4*>(dst)[1] = q1;
+                } else {
+                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j < cols_here && col0 + j < g.cols) {
+                            if (g.out_f32) reinterpret_cast<uint32_t*>(dst)[j] = w[j & 7];
+                            else reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
+                        }
+                    }
+                }
+            }
+        };
+
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
             const int tm = t % g.tiles_m, tn = t / g.tiles_m;
             const int acc = local % Cfg::ACC_STAGES;
@@ -349,110 +384,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int64_t row = static_cast<int64_t>(tm) * BM + row_in_tile;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int s = 0; s < nslab; ++s) {
-                const int c0 = s * cols_per_slab;
-                uint32_t r[32];
-                if (g.out_f32) tc_ld16(taddr + c0, r); else tc_ld32(taddr + c0, r);
-                tc_wait_ld();
-                if (Cfg::HALVES == 2 && (s + 1) * 2 == nslab) {   // the first half of the accumulator has been read out
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES]);
-                }
-                const int64_t col0 = static_cast<int64_t>(tn) * BN + c0;
-                const bool live = col0 < g.cols && static_cast<int64_t>(tm) * BM + sub * 32 < g.rows;
-                if (!live) continue;   // warp-uniform: the whole slab lies outside the crop
-                // ---- value chain -> 64 bytes per row, as 4 x 16 bytes ----
-                uint4 q[4];
-                if (!g.bias && g.raw_bf16 && !g.out_f32) {
-                    uint32_t w[16];
+            const int tile_row0 = tm * BM + sub * 32;
+            const int64_t colbase = static_cast<int64_t>(tn) * BN + half * SHARE;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * BN + half * SHARE;
+            const bool rows_live = tile_row0 < g.rows;
+            if (fast) {
+                uint32_t packed[CHUNKS * 16];
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + c * 32, r);
+                    tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                         if (scaled) p = __hmul2(p, alpha2);   // bf16 x bf16 is exact in FP32: one rounding, as in the FP32 chain
-                        w[j] = *reinterpret_cast<uint32_t*>(&p);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) q[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-                } else {
-                    float v[32];
-                    const int nv = cols_per_slab;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        v[j] = 0.f;
-                        if (j < nv) {
-                            float x = __uint_as_float(r[j]);
-                            if (g.raw_bf16) x = bf16_value(bf16_bits(x));
-                            if (scaled) {
-                                x = __fmul_rn(x, alpha);
-                                if (g.raw_bf16) x = bf16_value(bf16_bits(x));
-                            }
-                            if (g.bias && col0 + j < g.cols) {
-                                float b = g.bias_f32 ? __ldg(static_cast<const float*>(g.bias) + col0 + j)
-                                                     : bf16_value(__ldg(static_cast<const uint16_t*>(g.bias) + col0 + j));
-                                if (g.raw_bf16) b = bf16_value(bf16_bits(b));
-                                x = __fadd_rn(x, b);
-                                if (g.raw_bf16) x = bf16_value(bf16_bits(x));
-                            }
-                            v[j] = x;
-                        }
-                    }
-                    if (g.out_f32) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            q[j] = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
-                                              __float_as_uint(v[4 * j + 3]));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            q[j].x = bf16_bits(v[8 * j]) | (uint32_t(bf16_bits(v[8 * j + 1])) << 16);
-                            q[j].y = bf16_bits(v[8 * j + 2]) | (uint32_t(bf16_bits(v[8 * j + 3])) << 16);
-                            q[j].z = bf16_bits(v[8 * j + 4]) | (uint32_t(bf16_bits(v[8 * j + 5])) << 16);
-                            q[j].w = bf16_bits(v[8 * j + 6]) | (uint32_t(bf16_bits(v[8 * j + 7])) << 16);
-                        }
+                        packed[c * 16 + j] = *reinterpret_cast<uint32_t*>(&p);
                     }
                 }
-                if (g.tma_store) {
-                    uint8_t* dst = slab + buf * EPI_SLAB_BYTES;
-                    if (lane == 0) bulk_wait_read<Cfg::EPI_BUFS - 1>();   // the store that last read this buffer has drained it
-                    __syncwarp();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);   // accumulator share is in registers
+                if (rows_live) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)   // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
-                        *reinterpret_cast<uint4*>(dst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q[j];
-                    fence_async_shared();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&map_out, static_cast<int>(col0), tm * BM + sub * 32, dst);
-                        bulk_commit();
+                    for (int c = 0; c < CHUNKS * 2; ++c) {
+                        const int64_t col0 = colbase + c * 16;
+                        if (col0 < g.cols)
+                            emit(make_uint4(packed[c * 8], packed[c * 8 + 1], packed[c * 8 + 2], packed[c * 8 + 3]),
+                                 make_uint4(packed[c * 8 + 4], packed[c * 8 + 5], packed[c * 8 + 6], packed[c * 8 + 7]), row, col0, tile_row0, 16);
                     }
-                    if (++buf == Cfg::EPI_BUFS) buf = 0;
-                } else if (row < g.rows) {
-                    // unaligned output: plain stores, element-wise at the ragged edge
-                    const int esz = g.out_f32 ? 4 : 2;
-                    uint8_t* dst = static_cast<uint8_t*>(g.out) + (row * g.ldo + col0) * esz;
-                    if (col0 + cols_per_slab <= g.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                }
+            } else {
+                const int cols_per_slab = g.out_f32 ? 8 : 16;
+#pragma unroll 1
+                for (int c = 0; c < CHUNKS; ++c) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + c * 32, r);
+                    tc_wait_ld();
+                    if (c + 1 == CHUNKS) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);
+                    }
+                    if (!rows_live) continue;
+                    float v[32];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = q[j];
-                    } else {
-                        uint32_t w[16];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) { w[4 * j] = q[j].x; w[4 * j + 1] = q[j].y; w[4 * j + 2] = q[j].z; w[4 * j + 3] = q[j].w; }
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < cols_per_slab && col0 + j < g.cols) {
-                                if (g.out_f32) reinterpret_cast<uint32_t*>(dst)[j] = w[j & 15];
-                                else reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
-                            }
+                    for (int j = 0; j < 32; ++j) {
+                        const int64_t col = colbase + c * 32 + j;
+                        float x = __uint_as_float(r[j]);
+                        if (g.raw_bf16) x = bf16_value(bf16_bits(x));
+                        if (scaled) {
+                            x = __fmul_rn(x, alpha);
+                            if (g.raw_bf16) x = bf16_value(bf16_bits(x));
                         }
+                        if (g.bias && col < g.cols) {
+                            float b = g.bias_f32 ? __ldg(static_cast<const float*>(g.bias) + col)
+                                                 : bf16_value(__ldg(static_cast<const uint16_t*>(g.bias) + col));
+                            if (g.raw_bf16) b = bf16_value(bf16_bits(b));
+                            x = __fadd_rn(x, b);
+                            if (g.raw_bf16) x = bf16_value(bf16_bits(x));
+                        }
+                        v[j] = x;
+                    }
+#pragma unroll
+                    for (int sl = 0; sl < 4; ++sl) {          // up to four 32-byte slabs per 32 columns
+                        if (sl * cols_per_slab >= 32) break;
+                        const int j0 = sl * cols_per_slab;
+                        const int64_t col0 = colbase + c * 32 + j0;
+                        if (col0 >= g.cols) continue;
+                        uint4 q0, q1;
+                        if (g.out_f32) {
+                            q0 = make_uint4(__float_as_uint(v[j0]), __float_as_uint(v[j0 + 1]), __float_as_uint(v[j0 + 2]), __float_as_uint(v[j0 + 3]));
+                            q1 = make_uint4(__float_as_uint(v[j0 + 4]), __float_as_uint(v[j0 + 5]), __float_as_uint(v[j0 + 6]), __float_as_uint(v[j0 + 7]));
+                        } else {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) w[j] = bf16_bits(v[j0 + 2 * j]) | (uint32_t(bf16_bits(v[j0 + 2 * j + 1])) << 16);
+                            q0 = make_uint4(w[0], w[1], w[2], w[3]); q1 = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                        emit(q0, q1, row, col0, tile_row0, cols_per_slab);
                     }
                 }
             }
-            // every TMEM read of this warp has completed (wait::ld above): hand the rest of the accumulator back
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + Cfg::HALVES - 1]);
         }
         if (lane == 0) bulk_wait_all();
     }
@@ -493,17 +506,17 @@ static bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, i
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Output map for the epilogue's stores: boxes of 32 rows x 64 bytes, 64-byte swizzle; the bounds crop the tile.
+// Output map for the epilogue's stores: boxes of 32 rows x 32 bytes, 32-byte swizzle; the bounds crop the tile.
 static bool make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldo, bool f32) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const int esz = f32 ? 4 : 2;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo * esz)};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(64 / esz), 32};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(32 / esz), 32};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
