@@ -186,6 +186,53 @@ int nvfp4_rope(const void* x, void* out, const void* cos_t, const void* sin_t, i
 int nvfp4_swiglu(const void* gate, const void* up, const void* dout, void* out_or_dgate, void* dup, int64_t n,
                  nvfp4_stream_t stream);
 
+/*
+ * ---- frozen NVFP4 checkpoints in "Comfy" order as LoRA bases ------------------------------------------------------
+ * Payload bytes hold the even element in the HIGH nibble; block scales are E4M3 in the same 128 x 4 swizzle as above;
+ * one FP32 tensor scale.  These five entry points replace the run-time-compiled kernels the reference launches through
+ * the CUDA driver API (src/precision_lora/_packed_cuda.py:215-219, `launch(name, blocks, threads, *args)`).
+ *
+ * nvfp4_comfy_quantize: x [rows][cols] BF16 contiguous, cols % 128 == 0.  With signs128 != NULL every aligned run of
+ * 128 columns is first rotated by sign * H128 / sqrt(128).  tensor_scale[0] = max(amax / 2688, 1e-30); block scales are
+ * the software E4M3 RNE of max16 / (6 * tensor_scale); elements are rounded by the hardware RNE conversion, or with
+ * sr != 0 stochastically from mix32(element index ^ (seed + counter[0])) (counter nullable, device int32).  Writes
+ * packed [ceil16(rows)][cols / 2], scales for ceil128(rows) rows (rows past `rows` as zeros) and tensor_scale.
+ * amax_scratch: one device float, overwritten.  Replaces kernels rotate, amax_bf16 and quant (_packed_cuda.py:64-103)
+ * and their launcher quantize() (:228-243).
+ */
+int nvfp4_comfy_quantize(const void* x, int64_t rows, int64_t cols, const float* signs128, int sr, uint32_t seed,
+                         const int32_t* counter, uint8_t* packed, uint8_t* scales, float* tensor_scale, float* amax_scratch,
+                         nvfp4_stream_t stream);
+
+/* packed [n][k / 2] -> BF16 [n][k]: scale = bf16(g * e4m3(s)), value = bf16(e2m1 * scale).  k % 16 == 0.
+ * Replaces kernel dequant (_packed_cuda.py:56-63, launcher :221-225). */
+int nvfp4_comfy_dequantize(const uint8_t* packed, const uint8_t* scales, const float* tensor_scale, void* out, int64_t n,
+                           int64_t k, nvfp4_stream_t stream);
+
+/*
+ * The input-gradient operand of a packed weight W [n][k] without a dense copy: decode, multiply by signs128 along n,
+ * rotate each aligned run of 128 output features by H128 / sqrt(128), requantise (RNE) as [k][n].  n, k % 128 == 0.
+ * nvfp4_comfy_backward_scale computes that tensor's scale max(amax / 2688, 1e-30) (amax_scratch: one device float,
+ * overwritten); nvfp4_comfy_transpose_requant writes packed_t [k][n / 2] and scales_t against a given scale.
+ * Replace kernel transpose_rht_quant in its two modes and finish_scale (_packed_cuda.py:81-83,117-163; launchers
+ * transpose_rht_quant :266-273 and backward_scale :276-287).
+ */
+int nvfp4_comfy_backward_scale(const uint8_t* packed, const uint8_t* scales, const float* tensor_scale, const float* signs128,
+                               int64_t n, int64_t k, float* amax_scratch, float* backward_scale, nvfp4_stream_t stream);
+int nvfp4_comfy_transpose_requant(const uint8_t* packed, const uint8_t* scales, const float* tensor_scale,
+                                  const float* signs128, const float* backward_scale, uint8_t* packed_t, uint8_t* scales_t,
+                                  int64_t n, int64_t k, nvfp4_stream_t stream);
+/* scale[0] = max(amax[0] / 2688, 1e-30) with an IEEE division on the device (_packed_cuda.py:81-83). */
+int nvfp4_comfy_finish_scale(const float* amax, float* scale, nvfp4_stream_t stream);
+
+/*
+ * Rotary embedding by per-row 2 x 2 matrices: x, out [rows][heads][dim] BF16, rotation [rows][pairs][2][2] BF16; feature
+ * pairs (p, p + pairs) are multiplied by the matrix (its transpose when backward != 0), features from 2 * pairs on are
+ * copied.  Replaces kernel rope (_packed_cuda.py:104-114, launcher :251-257).
+ */
+int nvfp4_comfy_rope(const void* x, const void* rotation, void* out, int64_t rows, int heads, int dim, int pairs, int backward,
+                     nvfp4_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

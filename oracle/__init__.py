@@ -1,5 +1,5 @@
-"""ctypes front end of the CPU oracle (``liboracle.so``, built from ``nvfp4_oracle.c`` and
-``adamw_oracle.c`` by ``oracle/Makefile``).
+"""ctypes front end of the CPU oracle (``liboracle.so``, built from ``nvfp4_oracle.c``,
+``adamw_oracle.c`` and ``comfy_oracle.c`` by ``oracle/Makefile``).
 
 TEST INFRASTRUCTURE ONLY.  The oracle restates the reference's NVFP4 arithmetic on the CPU so that
 the CUDA kernels can be checked bit for bit; it is also the timed CPU baseline of the benchmark.
@@ -26,7 +26,7 @@ RNE, SR_HASH, SR_PHILOX, SR_MIX = 0, 1, 2, 3
 def build(force: bool = False) -> Path:
     """Compile the oracle with the system gcc (a second or two)."""
     target = _HERE / "liboracle.so"
-    sources = [_HERE / "nvfp4_oracle.c", _HERE / "adamw_oracle.c"]
+    sources = [_HERE / "nvfp4_oracle.c", _HERE / "adamw_oracle.c", _HERE / "comfy_oracle.c"]
     if force or not target.exists() or any(s.stat().st_mtime > target.stat().st_mtime for s in sources):
         subprocess.run(["make", "-C", str(_HERE), "-B", "liboracle.so"], check=True, capture_output=True)
     return target
@@ -61,7 +61,31 @@ def lib():
         L.orc_rescale.restype = None
         L.orc_rescale.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_int64, C.c_int, C.c_void_p]
+        _bind_comfy(L)
     return _LIB
+
+
+def _bind_comfy(L):
+    L.orc_comfy_bf.restype = C.c_float; L.orc_comfy_bf.argtypes = [C.c_uint16]
+    L.orc_comfy_rb.restype = C.c_uint16; L.orc_comfy_rb.argtypes = [C.c_float]
+    L.orc_comfy_f8.restype = C.c_float; L.orc_comfy_f8.argtypes = [C.c_uint8]
+    L.orc_comfy_rf8.restype = C.c_uint8; L.orc_comfy_rf8.argtypes = [C.c_float]
+    L.orc_comfy_f4.restype = C.c_float; L.orc_comfy_f4.argtypes = [C.c_int]
+    L.orc_comfy_mix.restype = C.c_uint32; L.orc_comfy_mix.argtypes = [C.c_uint32]
+    L.orc_comfy_rf4.restype = C.c_uint8; L.orc_comfy_rf4.argtypes = [C.c_float, C.c_uint32, C.c_int]
+    L.orc_comfy_swizzle.restype = C.c_int64; L.orc_comfy_swizzle.argtypes = [C.c_int64] * 3
+    L.orc_comfy_finish_scale.restype = C.c_float; L.orc_comfy_finish_scale.argtypes = [C.c_float]
+    L.orc_comfy_dequantize.restype = None
+    L.orc_comfy_dequantize.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int64, C.c_int64]
+    L.orc_comfy_rotate.restype = C.c_float
+    L.orc_comfy_rotate.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
+    L.orc_comfy_quantize.restype = C.c_float
+    L.orc_comfy_quantize.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p]
+    L.orc_comfy_transpose_requant.restype = C.c_float
+    L.orc_comfy_transpose_requant.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p,
+                                              C.c_int64, C.c_int64]
+    L.orc_comfy_rope.restype = None
+    L.orc_comfy_rope.argtypes = [C.c_void_p] * 3 + [C.c_int64] + [C.c_int] * 4
 
 
 def _ptr(a):
@@ -277,3 +301,71 @@ def philox(ctr, key):
     c = np.asarray(ctr, dtype=np.uint32); k = np.asarray(key, dtype=np.uint32); o = np.empty(4, dtype=np.uint32)
     lib().orc_philox4x32_10(_ptr(c), _ptr(k), _ptr(o))
     return o
+
+
+# ---- packed-checkpoint (Comfy order) LoRA backend --------------------------------------------------------------------
+def comfy_signs(seed: int = 0) -> np.ndarray:
+    """128 random +-1 floats of a PackedNVFP4Linear (src/precision_lora/packed.py:104-105)."""
+    import torch
+    gen = torch.Generator().manual_seed(int(seed) % (2 ** 63))
+    return (torch.randint(0, 2, (128,), generator=gen) * 2 - 1).float().numpy()
+
+
+def comfy_quantize(x_bits: np.ndarray, signs=None, *, sr=False, seed=0):
+    """x_bits: uint16 BF16 patterns [rows, cols], cols % 128 == 0 -> (q [rows16, cols/2], s flat swizzled, g)."""
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    rows, cols = x_bits.shape
+    assert cols % 128 == 0
+    rows16, rows128 = (rows + 15) // 16 * 16, round128(rows)
+    q = np.zeros((rows16, cols // 2), dtype=np.uint8)
+    s = np.zeros(rows128 * cols // 16, dtype=np.uint8)
+    sg = None if signs is None else np.ascontiguousarray(signs, dtype=np.float32)
+    g = lib().orc_comfy_quantize(_ptr(x_bits), rows, cols, _ptr(sg), int(sr), int(seed) & 0xFFFFFFFF, _ptr(q), _ptr(s))
+    return q, s, np.float32(g)
+
+
+def comfy_dequantize(q: np.ndarray, s: np.ndarray, g) -> np.ndarray:
+    """-> uint16 BF16 patterns [n, k]."""
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    n, k = q.shape[0], q.shape[1] * 2
+    y = np.zeros((n, k), dtype=np.uint16)
+    lib().orc_comfy_dequantize(_ptr(q), _ptr(np.ascontiguousarray(s, dtype=np.uint8)), float(g), _ptr(y), n, k)
+    return y
+
+
+def comfy_backward_scale(q, s, g, signs) -> np.float32:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    n, k = q.shape[0], q.shape[1] * 2
+    amax = lib().orc_comfy_transpose_requant(_ptr(q), _ptr(np.ascontiguousarray(s, dtype=np.uint8)), float(g),
+                                             _ptr(np.ascontiguousarray(signs, dtype=np.float32)), 0.0, None, None, n, k)
+    return np.float32(lib().orc_comfy_finish_scale(amax))
+
+
+def comfy_transpose_requant(q, s, g, signs, backward_scale):
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    n, k = q.shape[0], q.shape[1] * 2
+    qt = np.zeros((k, n // 2), dtype=np.uint8)
+    st = np.zeros(k * n // 16, dtype=np.uint8)
+    lib().orc_comfy_transpose_requant(_ptr(q), _ptr(np.ascontiguousarray(s, dtype=np.uint8)), float(g),
+                                      _ptr(np.ascontiguousarray(signs, dtype=np.float32)), float(backward_scale), _ptr(qt),
+                                      _ptr(st), n, k)
+    return qt, st
+
+
+def comfy_rope(x_bits, rot_bits, pairs, backward=False):
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    _, rows, heads, dim = x_bits.shape
+    y = np.zeros_like(x_bits)
+    lib().orc_comfy_rope(_ptr(x_bits), _ptr(np.ascontiguousarray(rot_bits, dtype=np.uint16)), _ptr(y), rows, heads, dim,
+                         int(pairs), int(backward))
+    return y
+
+
+def comfy_matmul(a, b, rows, cols) -> np.ndarray:
+    """BF16 result (as float32 values) of the block-scaled product of two Comfy-order packings (q, s, g):
+    float64 accumulation of code * block scale, times g_a * g_b in FP32, one rounding to BF16."""
+    (qa, sa, ga), (qb, sb, gb) = a, b
+    da = from_bf16_bits(comfy_dequantize(qa, sa, 1.0)).astype(np.float64)   # scale 1: e2m1 * e4m3 is exact in BF16
+    db = from_bf16_bits(comfy_dequantize(qb, sb, 1.0)).astype(np.float64)
+    acc = (da[:rows] @ db[:cols].T).astype(np.float32)
+    return from_bf16_bits(to_bf16_bits(acc * (np.float32(ga) * np.float32(gb))))

@@ -39,6 +39,12 @@ _SIGNATURES = {
     "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I32, P]),
     "nvfp4_swiglu": (I32, [P, P, P, P, P, I64, P]),
     "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
+    "nvfp4_comfy_quantize": (I32, [P, I64, I64, P, I32, U32, P, P, P, P, P, P]),
+    "nvfp4_comfy_dequantize": (I32, [P, P, P, P, I64, I64, P]),
+    "nvfp4_comfy_backward_scale": (I32, [P, P, P, P, I64, I64, P, P, P]),
+    "nvfp4_comfy_transpose_requant": (I32, [P, P, P, P, P, P, P, I64, I64, P]),
+    "nvfp4_comfy_finish_scale": (I32, [P, P, P]),
+    "nvfp4_comfy_rope": (I32, [P, P, P, I64, I32, I32, I32, I32, P]),
 }
 
 
