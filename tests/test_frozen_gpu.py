@@ -85,7 +85,7 @@ def test_pointwise_and_attention_cache(backend, tmp_path):
         def call(m):
             return m(x) if conv else m(x, x, x, need_weights=False)[0]
         dense, packed = call(original).float(), call(model).float()
-        assert ((packed - dense).norm() / dense.norm()).item() < 0.2
+        assert ((packed - dense).norm() / dense.norm()).item() < (0.15 if conv else 0.35)   # two FP4 layers around the softmax
         path = tmp_path / f"cache{i}.pt"
         save_frozen_cache(path, model, model_fingerprint="synthetic-v1")
         restored = load_frozen_cache(path, copy.deepcopy(original), expected_fingerprint="synthetic-v1")
