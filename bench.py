@@ -87,6 +87,25 @@ class ClockSampler:
                 "reasons": sorted(snake[r] for r in self.reasons)}
 
 
+class ProfilerRange:
+    """cudaProfilerStart/Stop around the timed region (--profiler-range), so that a profiler started with
+    --profile-from-start off sees exactly the timed launches."""
+
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+
+    def __enter__(self):
+        if self.enabled:
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStart()
+        return self
+
+    def __exit__(self, *_):
+        if self.enabled:
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -148,7 +167,7 @@ def run_quant(args, rank, world, device):
     barrier(world)
     launches = 0
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(torch.cuda.current_device()) as clk:
+    with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
         ev0.record()
         for i in range(args.steps):
             step(i)
@@ -244,20 +263,21 @@ C2 = dict(tokens=8192, d_in=4096, d_out=4096)
 FP4_NOMINAL_TFLOPS = 9000.0
 
 
-def time_kernel(fn, reps):
+def time_kernel(fn, reps, profiler_range=False):
     for _ in range(3):
         fn(0)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(reps):
-        fn(i)
-    e1.record()
-    torch.cuda.synchronize()
+    with ProfilerRange(profiler_range):
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
     return e0.elapsed_time(e1) / reps
 
 
-def gemm_microbench(device, tokens, d_in, d_out, reps=20):
+def gemm_microbench(device, tokens, d_in, d_out, reps=20, profiler_range=False):
     """The three GEMMs of one layer on rotated operand sets; returns (ms per triple, TFLOP/s, launches)."""
     from nvfp4_training._backend import quant
     g = torch.Generator(device=device).manual_seed(1234)
@@ -277,7 +297,7 @@ def gemm_microbench(device, tokens, d_in, d_out, reps=20):
         quant.matmul(a, w, rows=tokens, cols=d_out, output_dtype=torch.bfloat16)
         quant.matmul(ga, wt, rows=tokens, cols=d_in, output_dtype=torch.bfloat16)
         quant.raw_matmul(gt, xt, d_out, d_in)
-    ms = time_kernel(triple, reps)
+    ms = time_kernel(triple, reps, profiler_range)
     flops = 3 * 2.0 * tokens * d_in * d_out
     return ms, flops / (ms * 1e-3) / 1e12
 
@@ -329,7 +349,7 @@ def run_train(args, rank, world, device):
             graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
         barrier(world)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(torch.cuda.current_device()) as clk:
+        with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
             ev0.record()
             for _ in range(args.steps):
                 loss = graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
@@ -425,6 +445,154 @@ def cpu_train_baseline(cfg, budget_tokens=512):
                       "attention / embedding / head excluded"}
 
 
+# ------------------------------------------------------------------------------------------------
+# kernel workloads: the three GEMMs of one layer (config 2) and the compressed AdamW kernel alone
+# ------------------------------------------------------------------------------------------------
+def run_gemm(args, rank, world, device):
+    """C2: X[8192,4096] BF16, W[4096,4096] FP32, G[8192,4096] BF16; fprop + dgrad + wgrad on packed operands."""
+    from nvfp4_training import _native as nat
+    t, k, n = C2["tokens"], C2["d_in"], C2["d_out"]
+    barrier(world)
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        ms, tf = gemm_microbench(device, t, k, n, reps=args.steps, profiler_range=args.profiler_range)
+    ms = max_over_ranks(ms, world, device)
+    nat.check_status()
+    pk = peaks()
+    fp4_peak = 4.0 * pk["bf16_tflops"]
+    flops = 3 * 2.0 * t * k * n
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"metric": "nvfp4_linear_gemm_tflops", "value": world * tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out", "data": "synthetic",
+            "config": {"workload": "C2: fprop, dgrad, wgrad GEMMs of a 4096x4096 layer at 8192 tokens per GPU on pre-quantised operands "
+                                   "(token rows sharded across GPUs, no collective)", "l2": "3 rotated operand sets (~450 MB > L2)"},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf / fp4_peak, "traffic": None,
+                         "kernel": "gemm_kernel<256>", "kernel_ms": ms / 3, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)",
+                         "frac_of_nominal_9PF": tf / FP4_NOMINAL_TFLOPS},
+            "gpu_launches": 3 * args.steps, "clocks": clk.summary()}
+
+
+ADAM_N = 4096 * 8192   # one 4096x8192 weight: 33.5 M elements, 335 MB of traffic per launch
+
+
+def run_adamw(args, rank, world, device):
+    """The balanced profile's update kernel (FP16 master with SR, int8 m, uint8 sqrt-v, per-512 scales) on rotated tensors."""
+    from nvfp4_training import _native as nat
+    import math
+    n = ADAM_N
+    lr, b1, b2, wd = 3e-4, 0.9, 0.95, 0.1
+
+    def hyper(t):
+        return dict(lr=lr, decay=1 - lr * wd, b1=b1, b2=b2, c1=1 / (1 - b1 ** t), c2=1 / math.sqrt(1 - b2 ** t), eps=1e-8)
+    sets = []
+    for i in range(3):
+        g = torch.Generator(device=device).manual_seed(i)
+        w = (torch.randn(n, device=device, generator=g) * 0.02).half()
+        grad = (torch.randn(n, device=device, generator=g) * 1e-3).bfloat16()
+        sets.append(dict(p=w, grad=grad, m=torch.zeros(n, dtype=torch.int8, device=device), v=torch.zeros(n, dtype=torch.uint8, device=device),
+                         ms=torch.zeros(n // 512, device=device), vs=torch.zeros(n // 512, device=device),
+                         scale=torch.empty((), device=device)))
+    count = [0]
+
+    def opt_step(i):
+        count[0] += 1
+        t = count[0]
+        s = sets[i % 3]
+        nat.adamw_step(s["p"], 17, s["grad"], s["m"], s["v"], s["ms"], s["vs"], vbits=8, mbits=8, nonlinear_m=False, state_block=512,
+                       hyper=hyper(t), step=t, key=12345, grad_kind=1, scale_out=s["scale"])
+    for i in range(max(args.warmup, 3)):
+        opt_step(i)
+    barrier(world)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
+        ev0.record()
+        for i in range(args.steps):
+            opt_step(i)
+        ev1.record()
+        barrier(world)
+    ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps, world, device)
+    pk = peaks()
+    bytes_per = ADAM_N * (2 + 2 + 1 + 1 + 2 + 1 + 1) + ADAM_N // 512 * 16   # p, g, m, v in; p, m, v out; scales
+    gbs = bytes_per / (ms * 1e-3) / 1e9
+    return {"metric": "nvfp4_adamw_GBps", "value": world * gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 math on fp16/int8/uint8 state",
+            "data": "synthetic",
+            "config": {"workload": "compressed AdamW (balanced: half16_v8) on one 4096x8192 weight per GPU, BF16 gradient",
+                       "l2": "3 rotated parameter sets (1 GB > L2)"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                         "kernel": "adamw_kernel<17,8,false,false,512>", "kernel_ms": ms, "peak_source": pk["source"]},
+            "elements_per_s": ADAM_N / (ms * 1e-3), "gpu_launches": args.steps, "clocks": clk.summary()}
+
+
+# ------------------------------------------------------------------------------------------------
+# LoRA workloads: config 4 (GPT-2-small layout, bases re-packed to NVFP4) and config 5 (DiT trunk over packed checkpoints)
+# ------------------------------------------------------------------------------------------------
+def run_lora(args, rank, world, device):
+    from precision_lora import prepare_lora, capture_lora_step, lora_parameters
+    from nvfp4_training._workloads import lora_models as lm
+    packed = args.workload == "lora_packed"
+    torch.manual_seed(11 if packed else 7)
+    if packed:
+        blocks = args.blocks or 24
+        model = lm.DiT(blocks=blocks, backward_mode=args.backward_mode, device=device, seed=11)
+        model, opt = prepare_lora(model, mode="packed_nvfp4", rank=16, alpha=16, target_modules=lm.DIT_TARGETS, lr=1e-4)
+        tokens, n_text, dim = 4608, 512, 3072
+        gen = torch.Generator(device=device).manual_seed(11 + rank)
+        batches = [tuple(torch.randn(shape, device=device, generator=gen).bfloat16() for shape in ((1, tokens - n_text, dim), (1, n_text, dim)))
+                   + (torch.randn((1, tokens - n_text, dim), device=device, generator=gen),) for _ in range(2)]
+        loss_fn = lm.denoise_loss
+        base_params = blocks * (3 * dim * dim + dim * dim + 2 * 12288 * dim)
+        name = (f"C5: {blocks}-block DiT trunk (d 3072, 24 heads, GELU FFN 12288) over packed NVFP4 checkpoints, 4096 image + 512 text "
+                f"tokens, LoRA r16 on qkv/out/up/down, batch 1, mode packed_nvfp4, backward {args.backward_mode}, eager")
+    else:
+        blocks = args.blocks or 12
+        model = lm.GPT2Small(layers=blocks).to(device).bfloat16()
+        model, opt = prepare_lora(model, mode="nvfp4", rank=16, alpha=16, target_modules=lm.GPT2_TARGETS, lr=2e-4)
+        tokens = 16 * 1024
+        gen = torch.Generator().manual_seed(7 + rank)
+        ids = torch.randint(0, 50257, (2, 16, 1025), generator=gen).to(device)
+        batches = [(ids[i, :, :-1].contiguous(), ids[i, :, 1:].contiguous()) for i in range(2)]
+        loss_fn = lm.lm_loss
+        base_params = blocks * (3 * 768 * 768 + 768 * 768 + 2 * 3072 * 768)
+        name = (f"C4: GPT-2-small layout ({blocks} blocks, d 768, vocab 50257), bases re-packed to NVFP4 with RHT, LoRA r16 on "
+                "qkv/proj/up/down, 16 x 1024 tokens, mode nvfp4, update captured as one CUDA graph")
+    torch.cuda.reset_peak_memory_stats()
+
+    def eager(i):
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = loss_fn(model, *batches[i % 2])
+        loss.backward()
+        opt.step()
+        return loss
+    graph = None
+    if not packed:
+        graph = capture_lora_step(model, opt, loss_fn, *batches[0])
+    run = (lambda i: graph.step(*batches[i % 2])) if graph is not None else eager
+    for i in range(args.warmup):
+        run(i)
+    barrier(world)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
+        ev0.record()
+        for i in range(args.steps):
+            loss = run(i)
+        ev1.record()
+        barrier(world)
+    ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps, world, device)
+    final = float(loss.item())
+    if graph is not None:
+        graph.close()
+    peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
+    base_flops = 4.0 * base_params * tokens   # forward + input gradient of the frozen bases
+    return {"metric": "lora_tokens_per_s", "value": world * tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 bases (fp32 accumulate), bf16 adapters / attention", "data": "synthetic",
+            "config": {"workload": name, "l2": "frozen bases exceed the 126 MB L2" if packed else "activations of 16384 tokens exceed the L2"},
+            "s_per_update": ms * 1e-3, "peak_GiB": peak_gib, "base_gemm_tflops": base_flops / (ms * 1e-3) / 1e12, "loss": final,
+            "adapter_parameters": sum(p.numel() for p in lora_parameters(model)), "clocks": clk.summary()}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return None
@@ -446,7 +614,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="train", choices=("train", "quant"))
+    ap.add_argument("--workload", default="train", choices=("train", "quant", "gemm", "adamw", "lora_nvfp4", "lora_packed"))
+    ap.add_argument("--profiler-range", action="store_true", help="bracket the timed region with cudaProfilerStart/Stop")
+    ap.add_argument("--backward-mode", default="recompute", choices=("recompute", "cache"), help="lora_packed only")
+    ap.add_argument("--blocks", type=int, default=0, help="override the block count of the LoRA workloads (smoke runs only)")
     ap.add_argument("--layers", type=int, default=0, help="override the decoder depth (smoke runs only; the metric needs the default)")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
@@ -465,7 +636,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    line = {"quant": run_quant, "train": run_train}[args.workload](args, rank, world, device)
+    runners = {"quant": run_quant, "train": run_train, "gemm": run_gemm, "adamw": run_adamw, "lora_nvfp4": run_lora, "lora_packed": run_lora}
+    line = runners[args.workload](args, rank, world, device)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
