@@ -44,7 +44,8 @@ template <int BN> struct GemmCfg {
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;
-    static constexpr int HALVES = (BN == 256) ? 2 : 1;   // parts an accumulator is released in
+    static constexpr int HALVES = 1;   // parts an accumulator is released in (the epilogue warps drain their shares concurrently,
+                                       // so a split release only adds narrow MMAs to the first k-tile)
     static constexpr int SFA_COLS = 16;             // 4 k-blocks x 4 columns
     static constexpr int SFB_COLS = 4 * (BN / 32);  // 4 k-blocks x BN/32 columns
     static constexpr int ACC_COLS = ACC_STAGES * BN;
