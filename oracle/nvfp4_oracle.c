@@ -20,10 +20,12 @@
  * Build: gcc -O2 -fopenmp -ffp-contract=off -fno-fast-math -shared -fPIC (see oracle/Makefile).
  * -ffp-contract=off mirrors the reference's --fmad=false: every * + - / is one IEEE FP32 rounding.
  *
- * Parity status: the reference ships no golden byte vectors and none of its code can execute
- * without an SM120 GPU, so bit patterns are pinned only through the known-answer relations its
- * tests state (zero stays zero, finish_scale correctly rounded, transpose-requant identity, SR
- * statistics) and through published known-answer vectors for Philox4x32-10.
+ * Parity status: PINNED.  The reference's Triton kernels (dual, weight pair, single, rescale) were executed on
+ * Triton's CPU interpreter from the reference's own source tree (tests/golden/make_golden.py, three documented
+ * interpreter fixes in tests/golden/triton_cpu_shim.py) and their outputs are committed as
+ * tests/golden/quant_reference.npz; this file reproduces them bit for bit (tests/test_oracle_golden.py).  The CUDA-only
+ * row / transposed kernels compute the same function as those Triton kernels.  Philox4x32-10 is pinned by the
+ * Random123 known-answer vectors.  GEMM bit patterns are a cuBLASLt property and are not pinned by the reference.
  */
 #include <math.h>
 #include <stdint.h>
