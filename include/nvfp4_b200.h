@@ -34,6 +34,9 @@ enum {
 /* element type codes */
 enum { NVFP4_F32 = 0, NVFP4_BF16 = 1, NVFP4_F16 = 2, NVFP4_E4M3 = 3 };
 
+/* flag bits of nvfp4_gemm's raw_bf16 argument */
+enum { NVFP4_GEMM_RAW_BF16 = 1, NVFP4_GEMM_SINGLE_CTA = 2 };
+
 /* per-orientation flags of the quantiser */
 enum {
     NVFP4_Q_RHT = 1,        /* sign * H16 / 4 over each 16 contraction elements before scaling */
@@ -123,8 +126,10 @@ int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* 
  *   a [M][K/2], b [N][K/2]: e2m1 payloads (low nibble = even element), K-major; sfa, sfb: swizzled ue4m3 block
  *   scales as the quantiser writes them; M, N, K multiples of 128; FP32 accumulation (tcgen05, TMEM).
  *   pts_a, pts_b: device FP32 tensor scales, alpha = pts_a * pts_b; both null = store the raw accumulator.
- *   raw_bf16 != 0 reproduces the reference's BF16 chain: bf16(acc), alpha -> bf16, bf16(raw * alpha),
- *   bf16(y + bf16(bias)); raw_bf16 == 0 is the FP32 chain acc * alpha (+ bias).
+ *   raw_bf16 is a flag word.  Bit 0 set reproduces the reference's BF16 chain: bf16(acc), alpha -> bf16,
+ *   bf16(raw * alpha), bf16(y + bf16(bias)); bit 0 clear is the FP32 chain acc * alpha (+ bias).
+ *   NVFP4_GEMM_SINGLE_CTA (bit 1) keeps every tile on one SM; by default shapes with M and N multiples of 256 run on
+ *   pairs of SMs (thread-block clusters of two, 256-row MMAs), which gives the same results.
  *   out: FP32 or BF16, row stride ldo elements.  status: nullable device int, set to NVFP4_ERR_TIMEOUT if a
  *   bounded device-side wait expired (the kernel then returns early instead of hanging).
  * Replaces torch._scaled_mm on float4_e2m1fn_x2 operands (src/nvfp4_training/_backend/nvfp4_fast_v2.py:208-215,

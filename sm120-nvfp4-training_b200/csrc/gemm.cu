@@ -37,12 +37,17 @@ constexpr int EPI_SLAB_BYTES = 1024;  // 32 rows x 32 bytes per epilogue warp
 constexpr int EPI_WARPS = 8;
 constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
-template <int BN> struct GemmCfg {
-    static constexpr int B_STAGE_BYTES = BN * 128;
+// PAIR: two CTAs of a cluster work on one 256 x 256 tile with tcgen05.mma.cta_group::2 (256-row MMAs): each CTA loads
+// its own 128 rows of A and its own 128 of the tile's 256 rows of B, holds the accumulator of its 128 rows, and the
+// leader CTA (cluster rank 0) issues every MMA for both.
+template <int BN, bool PAIR> struct GemmCfg {
+    static_assert(!PAIR || BN == 256, "paired CTAs work on 256 x 256 tiles");
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;                 // rows of B this CTA loads per k-tile
+    static constexpr int B_STAGE_BYTES = B_ROWS * 128;
     static constexpr int SFA_STAGE_BYTES = 4 * SF_BLOCK;
-    static constexpr int SFB_STAGE_BYTES = (BN / 128) * 4 * SF_BLOCK;
+    static constexpr int SFB_STAGE_BYTES = (BN / 128) * 4 * SF_BLOCK;  // every CTA needs the scales of all BN columns
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int STAGES = PAIR ? 5 : (BN == 256) ? 4 : 6;
     static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;
     static constexpr int HALVES = 1;   // parts an accumulator is released in (the epilogue warps drain their shares concurrently,
                                        // so a split release only adds narrow MMAs to the first k-tile)
@@ -54,8 +59,9 @@ template <int BN> struct GemmCfg {
     static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
     static constexpr int TMEM_COLS = 512;
     static constexpr int EPI_BYTES = EPI_WARPS * EPI_SLAB_BYTES;
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * SF_BUFS + ACC_STAGES + ACC_STAGES * HALVES;
+    static constexpr int NUM_BARS = 2 * STAGES + (PAIR ? STAGES : 0) + 2 * SF_BUFS + ACC_STAGES + ACC_STAGES * HALVES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static constexpr int CTAS = PAIR ? 2 : 1;
     static_assert(ACC_COLS + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
     static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -123,6 +129,41 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// ---- forms used by paired CTAs (cluster of two) ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t leader_addr(const void* p) {   // the same shared-memory offset in cluster rank 0
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(smem_u32(p)));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(bar)) : "memory");
+}
+// tile load into this CTA's shared memory whose bytes are counted on the leader CTA's barrier (no multicast)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_addr(bar)) : "memory");
+}
+// arrive on the barrier at this offset in BOTH CTAs once every MMA issued so far has completed
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                            uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
                                        uint32_t tmem_sfa, uint32_t tmem_sfb) {
     asm volatile(
@@ -160,15 +201,15 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
     return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ uint32_t instr_desc(int n) {  // e2m1 x e2m1, ue4m3 scales, K-major A and B, M = 128
-    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+__device__ __forceinline__ uint32_t instr_desc(int n, int m = BM) {  // e2m1 x e2m1, ue4m3 scales, K-major A and B
+    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_out, const GemmArgs g) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* epi_smem = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
@@ -179,28 +220,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint64_t* sf_empty = sf_full + Cfg::SF_BUFS;
     uint64_t* acc_full = sf_empty + Cfg::SF_BUFS;
     uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;  // [ACC_STAGES][HALVES]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + Cfg::ACC_STAGES * Cfg::HALVES);
+    uint64_t* sf_landed = acc_empty + Cfg::ACC_STAGES * Cfg::HALVES;   // PAIR only: this CTA's scale blocks of a stage
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_landed + (PAIR ? Cfg::STAGES : 0));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // PAIR: rank 0 of the cluster is the leader.  Barriers that gate the MMA issue (full, sf_full, acc_empty) are the
+    // leader's and count arrivals of both CTAs; barriers that release resources (empty, sf_empty, acc_full) exist in
+    // both CTAs and are arrived on together by one committed tcgen05 operation.
+    const int rank = PAIR ? static_cast<int>(cluster_rank()) : 0;
+    const bool leader = rank == 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
-        for (int s = 0; s < Cfg::SF_BUFS; ++s) { mbar_init(&sf_full[s], 4); mbar_init(&sf_empty[s], 1); }
+        if constexpr (PAIR) for (int s = 0; s < Cfg::STAGES; ++s) mbar_init(&sf_landed[s], 1);
+        for (int s = 0; s < Cfg::SF_BUFS; ++s) { mbar_init(&sf_full[s], 4 * Cfg::CTAS); mbar_init(&sf_empty[s], 1); }
         for (int a = 0; a < Cfg::ACC_STAGES; ++a) mbar_init(&acc_full[a], 1);
-        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], EPI_WARPS / Cfg::HALVES);
+        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], EPI_WARPS * Cfg::CTAS / Cfg::HALVES);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(Cfg::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {   // the same warp of both CTAs allocates the same columns in both tensor memories
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(Cfg::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(Cfg::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();   // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int total_tiles = g.tiles_m * g.tiles_n;
+    const int total_tiles = g.tiles_m * g.tiles_n;     // PAIR: tiles_m counts 256-row tiles
     const int kb_total = g.K / 64;
+    const int first_tile = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -208,23 +264,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int stage = 0; uint32_t phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int tm = t % g.tiles_m, tn = t / g.tiles_m;
+            for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
+                const int tm = (t % g.tiles_m) * Cfg::CTAS + rank, tn = t / g.tiles_m;   // tm: this CTA's 128-row block
                 for (int kt = 0; kt < g.k_tiles; ++kt) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = smem + stage * Cfg::STAGE_BYTES;
                     const int kblocks = min(4, kb_total - kt * 4);
                     const uint32_t sf_bytes = kblocks * SF_BLOCK;
-                    mbar_expect_tx(&full[stage], A_STAGE_BYTES + Cfg::B_STAGE_BYTES + sf_bytes * (1 + BN / 128));
-                    tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[stage]);
-                    tma_load_2d(st + A_STAGE_BYTES, &map_b, kt * 128, tn * BN, &full[stage]);
+                    uint64_t* sf_bar;
+                    if constexpr (PAIR) {
+                        // operand bytes of both CTAs are counted on the leader's barrier; scale blocks on this CTA's own
+                        if (leader) mbar_expect_tx(&full[stage], 2 * (A_STAGE_BYTES + Cfg::B_STAGE_BYTES));
+                        sf_bar = &sf_landed[stage];
+                        mbar_expect_tx(sf_bar, sf_bytes * (1 + BN / 128));
+                        tma_load_2d_pair(st, &map_a, kt * 128, tm * BM, &full[stage]);
+                        tma_load_2d_pair(st + A_STAGE_BYTES, &map_b, kt * 128, tn * BN + rank * Cfg::B_ROWS, &full[stage]);
+                    } else {
+                        sf_bar = &full[stage];
+                        mbar_expect_tx(&full[stage], A_STAGE_BYTES + Cfg::B_STAGE_BYTES + sf_bytes * (1 + BN / 128));
+                        tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[stage]);
+                        tma_load_2d(st + A_STAGE_BYTES, &map_b, kt * 128, tn * BN, &full[stage]);
+                    }
                     bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES,
-                              g.sfa + (static_cast<int64_t>(tm) * kb_total + kt * 4) * SF_BLOCK, sf_bytes, &full[stage]);
+                              g.sfa + (static_cast<int64_t>(tm) * kb_total + kt * 4) * SF_BLOCK, sf_bytes, sf_bar);
 #pragma unroll
                     for (int nb = 0; nb < BN / 128; ++nb)
                         bulk_load(st + A_STAGE_BYTES + Cfg::B_STAGE_BYTES + Cfg::SFA_STAGE_BYTES + nb * 4 * SF_BLOCK,
                                   g.sfb + (static_cast<int64_t>(tn * (BN / 128) + nb) * kb_total + kt * 4) * SF_BLOCK, sf_bytes,
-                                  &full[stage]);
+                                  sf_bar);
                     ++issued;
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -236,19 +303,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int i = 0; i < pending; ++i) {
                     if (--s < 0) { s = Cfg::STAGES - 1; ph ^= 1; }
                     const long long t0 = clock64();
-                    while (!mbar_try(&full[s], ph) && clock64() - t0 < WAIT_CYCLES / 8) {}
+                    // PAIR: only the scale-block barrier is local; the operand tiles were issued before it
+                    while (!mbar_try(PAIR ? &sf_landed[s] : &full[s], ph) && clock64() - t0 < WAIT_CYCLES / 8) {}
                 }
+                if constexpr (PAIR) { const long long t0 = clock64(); while (clock64() - t0 < 400000) {} }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            const uint32_t idesc_full = instr_desc(BN), idesc_half = instr_desc(BN / 2);
+        if (lane == 0 && leader) {
+            const uint32_t idesc_full = instr_desc(BN, BM * Cfg::CTAS), idesc_half = instr_desc(BN / 2, BM * Cfg::CTAS);
             int stage = 0; uint32_t phase = 0;
             int sfb = 0; uint32_t sf_phase = 0;
             int local = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            auto mma = [](uint32_t d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc, uint32_t tsfa, uint32_t tsfb) {
+                if constexpr (PAIR) tc_mma_pair(d, da, db, idesc, acc, tsfa, tsfb); else tc_mma(d, da, db, idesc, acc, tsfa, tsfb);
+            };
+            auto commit = [](uint64_t* bar) { if constexpr (PAIR) tc_commit_pair(bar); else tc_commit(bar); };
+            for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++local) {
                 const int acc = local % Cfg::ACC_STAGES;
                 const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
                 const uint32_t tmem_acc = tmem_base + acc * BN;
@@ -268,22 +341,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             tc_fence_after();
                             constexpr int NH = BN / Cfg::HALVES;
                             for (int kb = 0; kb < kblocks; ++kb)
-                                tc_mma(tmem_acc + h * NH, operand_desc(sa + kb * 32), operand_desc(sb + h * NH * 128 + kb * 32),
+                                mma(tmem_acc + h * NH, operand_desc(sa + kb * 32), operand_desc(sb + h * NH * 128 + kb * 32),
                                        Cfg::HALVES == 2 ? idesc_half : idesc_full, kb > 0 ? 1u : 0u, sfa_tmem + kb * 4,
                                        sfb_tmem + kb * (BN / 32) + h * (NH / 32));
                         }
                         if (!ok) break;
                     } else {
                         for (int kb = 0; kb < kblocks; ++kb)
-                            tc_mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, 1u,
+                            mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, 1u,
                                    sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
                     }
-                    tc_commit(&empty[stage]);
-                    tc_commit(&sf_empty[sfb]);
+                    commit(&empty[stage]);
+                    commit(&sf_empty[sfb]);
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
                     if (++sfb == Cfg::SF_BUFS) { sfb = 0; sf_phase ^= 1; }
                 }
-                if (ok) tc_commit(&acc_full[acc]);
+                if (ok) commit(&acc_full[acc]);
             }
         }
     } else if (warp < 6) {
@@ -293,9 +366,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         int stage = 0; uint32_t phase = 0;
         int sfb = 0; uint32_t sf_phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
             for (int kt = 0; kt < g.k_tiles; ++kt) {
-                if (!mbar_wait(&full[stage], phase, abort_flag) || !mbar_wait(&sf_empty[sfb], sf_phase ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(PAIR ? &sf_landed[stage] : &full[stage], phase, abort_flag) ||
+                    !mbar_wait(&sf_empty[sfb], sf_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint8_t* ssfa = smem + stage * Cfg::STAGE_BYTES + A_STAGE_BYTES + Cfg::B_STAGE_BYTES;
                 const uint8_t* ssfb = ssfa + Cfg::SFA_STAGE_BYTES;
@@ -324,7 +398,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&sf_full[sfb]); mbar_arrive(&empty[stage]); }
+                if (lane == 0) {
+                    if (PAIR && !leader) mbar_arrive_leader(&sf_full[sfb]); else mbar_arrive(&sf_full[sfb]);
+                    mbar_arrive(&empty[stage]);
+                }
                 if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
                 if (++sfb == Cfg::SF_BUFS) { sfb = 0; sf_phase ^= 1; }
             }
@@ -378,8 +455,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         };
 
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-            const int tm = t % g.tiles_m, tn = t / g.tiles_m;
+        auto release_acc = [&](uint64_t* bar) { if (PAIR && !leader) mbar_arrive_leader(bar); else mbar_arrive(bar); };
+        for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++local) {
+            const int tm = (t % g.tiles_m) * Cfg::CTAS + rank, tn = t / g.tiles_m;
             const int acc = local % Cfg::ACC_STAGES;
             const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
@@ -405,7 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);   // accumulator share is in registers
+                if (lane == 0) release_acc(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);   // accumulator share is in registers
                 if (rows_live) {
 #pragma unroll
                     for (int c = 0; c < CHUNKS * 2; ++c) {
@@ -425,7 +503,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (c + 1 == CHUNKS) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);
+                        if (lane == 0) release_acc(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);
                     }
                     if (!rows_live) continue;
                     float v[32];
@@ -473,10 +551,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();   // neither CTA leaves while the other may still touch its memory or barriers
     if (threadIdx.x == 0 && *abort_flag && g.status) atomicExch(g.status, NVFP4_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(Cfg::TMEM_COLS) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(Cfg::TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
@@ -521,14 +603,14 @@ static bool make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t col
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, GemmArgs& g, cudaStream_t st) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, PAIR>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_gemm: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
         configured[dev] = true;
     }
@@ -536,8 +618,26 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     if (dev < 64 && !sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     const int sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
     g.tiles_n = g.N / BN;
-    const int grid = std::min(g.tiles_m * g.tiles_n, sms);
-    gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, mo, g);
+    g.tiles_m = g.M / (BM * Cfg::CTAS);
+    if constexpr (PAIR) {
+        // persistent clusters of two CTAs (one per SM of a pair); an odd SM count leaves one SM idle
+        const int clusters = std::min(g.tiles_m * g.tiles_n, sms / 2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(clusters * 2));
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, PAIR>, ma, mb, mo, g);
+        NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_gemm: cluster launch failed: %s", cudaGetErrorString(e));
+    } else {
+        const int grid = std::min(g.tiles_m * g.tiles_n, sms);
+        gemm_kernel<BN, PAIR><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, mo, g);
+    }
     return launch_status("nvfp4_gemm");
 }
 
@@ -561,19 +661,21 @@ extern "C" int nvfp4_gemm(const uint8_t* a, const uint8_t* sfa, const float* pts
         NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_gemm: operands and scales must be 16-byte aligned");
     GemmArgs g{};
     g.sfa = sfa; g.sfb = sfb; g.pts_a = pts_a; g.pts_b = pts_b; g.bias = bias; g.out = out; g.status = status;
-    g.ldo = ldo; g.bias_f32 = bias_dtype == NVFP4_F32; g.out_f32 = out_dtype == NVFP4_F32; g.raw_bf16 = raw_bf16 != 0;
+    g.ldo = ldo; g.bias_f32 = bias_dtype == NVFP4_F32; g.out_f32 = out_dtype == NVFP4_F32; g.raw_bf16 = (raw_bf16 & 1) != 0;
     g.M = static_cast<int>(M); g.N = static_cast<int>(N); g.K = static_cast<int>(K);
     g.rows = static_cast<int>(rows); g.cols = static_cast<int>(cols);
-    g.tiles_m = g.M / BM; g.k_tiles = (g.K + BK - 1) / BK;
+    g.k_tiles = (g.K + BK - 1) / BK;
     const int bn = (N % 256 == 0) ? 256 : 128;
+    const bool pair = bn == 256 && M % 256 == 0 && !(raw_bf16 & NVFP4_GEMM_SINGLE_CTA);
     const int esz = g.out_f32 ? 4 : 2;
     // the bulk-tensor store needs a 16-byte aligned base and row pitch; anything else takes the plain-store epilogue
     g.tma_store = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo * esz) % 16 == 0;
     CUtensorMap ma, mb, mo;
-    NVFP4_REQUIRE(make_operand_map(&ma, a, M, K, BM) && make_operand_map(&mb, b, N, K, bn), NVFP4_ERR_LAUNCH,
+    NVFP4_REQUIRE(make_operand_map(&ma, a, M, K, BM) && make_operand_map(&mb, b, N, K, pair ? 128 : bn), NVFP4_ERR_LAUNCH,
                   "nvfp4_gemm: cuTensorMapEncodeTiled failed or is unavailable");
     if (g.tma_store && !make_out_map(&mo, out, rows, cols, ldo, g.out_f32)) g.tma_store = 0;
     if (!g.tma_store) mo = ma;  // unused by the kernel in this mode, but the parameter must hold a valid map
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    return bn == 256 ? launch_gemm<256>(ma, mb, mo, g, st) : launch_gemm<128>(ma, mb, mo, g, st);
+    if (pair) return launch_gemm<256, true>(ma, mb, mo, g, st);
+    return bn == 256 ? launch_gemm<256, false>(ma, mb, mo, g, st) : launch_gemm<128, false>(ma, mb, mo, g, st);
 }

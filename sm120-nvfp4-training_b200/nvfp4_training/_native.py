@@ -6,6 +6,7 @@ library.  There is no CPU or eager fallback: a missing library raises at first u
 from __future__ import annotations
 
 import ctypes as C
+import os
 import re
 from pathlib import Path
 
@@ -185,7 +186,11 @@ def check_status(device=None) -> None:
             raise RuntimeError(f"NVFP4 kernel on cuda:{idx} reported status {code} (bounded device-side wait expired)")
 
 
-def gemm(a, sfa, pts_a, b, sfb, pts_b, *, rows, cols, out_dtype=torch.bfloat16, bias=None, raw_bf16=True, out=None):
+GEMM_SINGLE_CTA = 2
+_PAIR = os.environ.get("NVFP4_GEMM_PAIR", "1") != "0"   # NVFP4_GEMM_PAIR=0 keeps every GEMM on single-SM tiles
+
+
+def gemm(a, sfa, pts_a, b, sfb, pts_b, *, rows, cols, out_dtype=torch.bfloat16, bias=None, raw_bf16=True, out=None, pair=None):
     """out[rows, cols] = crop(A @ B.T) * (pts_a * pts_b) (+ bias); a [M, K/2], b [N, K/2] packed payloads."""
     M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
     if b.shape[1] != a.shape[1]:
@@ -195,7 +200,8 @@ def gemm(a, sfa, pts_a, b, sfb, pts_b, *, rows, cols, out_dtype=torch.bfloat16, 
     with torch.cuda.device(a.device):
         check(lib().nvfp4_gemm(a.data_ptr(), sfa.data_ptr(), ptr(pts_a), b.data_ptr(), sfb.data_ptr(), ptr(pts_b), M, N, K,
                                ptr(bias), dtype_code(bias) if bias is not None else 0, out.data_ptr(), dtype_code(out),
-                               out.stride(0), rows, cols, int(bool(raw_bf16)), status_word(a.device).data_ptr(), stream_of(a)))
+                               out.stride(0), rows, cols, int(bool(raw_bf16)) | (0 if (_PAIR if pair is None else pair) else GEMM_SINGLE_CTA),
+                               status_word(a.device).data_ptr(), stream_of(a)))
     return out
 
 
