@@ -48,21 +48,26 @@ template <int BN, bool PAIR> struct GemmCfg {
     static constexpr int SFB_STAGE_BYTES = (BN / 128) * 4 * SF_BLOCK;  // every CTA needs the scales of all BN columns
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
     static constexpr int STAGES = PAIR ? 5 : (BN == 256) ? 4 : 6;
-    static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;
-    static constexpr int HALVES = 1;   // parts an accumulator is released in (the epilogue warps drain their shares concurrently,
-                                       // so a split release only adds narrow MMAs to the first k-tile)
+    // Two accumulator stages.  Two 256-column accumulators and the scale buffers do not fit the 512 columns of tensor
+    // memory, so with BN = 256 the stages OVERLAP by 96 columns: stage 0 = columns [0, 256), stage 1 = [160, 416),
+    // two scale buffers of 48 columns behind them.  The epilogue reads the shared 96 columns first (the last 96 of a
+    // stage-0 tile, the first 96 of a stage-1 tile) and only that part gates the next tile's MMAs; the rest of the
+    // drain and all stores run under the next mainloop.
+    static constexpr bool OVERLAP = BN == 256;
+    static constexpr int ACC_STAGES = 2;
+    static constexpr int ACC_STRIDE = OVERLAP ? 160 : BN;
+    static constexpr int SHARED_CHUNKS = OVERLAP ? (BN - ACC_STRIDE) / 32 : 0;   // 32-column chunks both stages use
     static constexpr int SFA_COLS = 16;             // 4 k-blocks x 4 columns
     static constexpr int SFB_COLS = 4 * (BN / 32);  // 4 k-blocks x BN/32 columns
-    static constexpr int ACC_COLS = ACC_STAGES * BN;
-    static constexpr int SF_BUFS = 3;
-    static constexpr int SF_BASE = ACC_COLS;
     static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
+    static constexpr int SF_BASE = ACC_STRIDE + BN;                     // 416 or 256
+    static constexpr int SF_BUFS = OVERLAP ? 2 : 3;                     // scale buffers, one k-tile each
     static constexpr int TMEM_COLS = 512;
     static constexpr int EPI_BYTES = EPI_WARPS * EPI_SLAB_BYTES;
-    static constexpr int NUM_BARS = 2 * STAGES + (PAIR ? STAGES : 0) + 2 * SF_BUFS + ACC_STAGES + ACC_STAGES * HALVES;
+    static constexpr int NUM_BARS = 2 * STAGES + (PAIR ? STAGES : 0) + 2 * SF_BUFS + 2 * ACC_STAGES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
     static constexpr int CTAS = PAIR ? 2 : 1;
-    static_assert(ACC_COLS + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
+    static_assert(SF_BASE + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
     static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
@@ -219,8 +224,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint64_t* sf_full = empty + Cfg::STAGES;
     uint64_t* sf_empty = sf_full + Cfg::SF_BUFS;
     uint64_t* acc_full = sf_empty + Cfg::SF_BUFS;
-    uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;  // [ACC_STAGES][HALVES]
-    uint64_t* sf_landed = acc_empty + Cfg::ACC_STAGES * Cfg::HALVES;   // PAIR only: this CTA's scale blocks of a stage
+    uint64_t* acc_empty = acc_full + Cfg::ACC_STAGES;  // [ACC_STAGES]; OVERLAP uses [0] only: "shared columns drained"
+    uint64_t* sf_landed = acc_empty + Cfg::ACC_STAGES;   // PAIR only: this CTA's scale blocks of a stage
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_landed + (PAIR ? Cfg::STAGES : 0));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -235,7 +240,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if constexpr (PAIR) for (int s = 0; s < Cfg::STAGES; ++s) mbar_init(&sf_landed[s], 1);
         for (int s = 0; s < Cfg::SF_BUFS; ++s) { mbar_init(&sf_full[s], 4 * Cfg::CTAS); mbar_init(&sf_empty[s], 1); }
         for (int a = 0; a < Cfg::ACC_STAGES; ++a) mbar_init(&acc_full[a], 1);
-        for (int a = 0; a < Cfg::ACC_STAGES * Cfg::HALVES; ++a) mbar_init(&acc_empty[a], EPI_WARPS * Cfg::CTAS / Cfg::HALVES);
+        for (int a = 0; a < Cfg::ACC_STAGES; ++a) mbar_init(&acc_empty[a], EPI_WARPS * Cfg::CTAS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,7 +317,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0 && leader) {
-            const uint32_t idesc_full = instr_desc(BN, BM * Cfg::CTAS), idesc_half = instr_desc(BN / 2, BM * Cfg::CTAS);
+            const uint32_t idesc_full = instr_desc(BN, BM * Cfg::CTAS);
             int stage = 0; uint32_t phase = 0;
             int sfb = 0; uint32_t sf_phase = 0;
             int local = 0;
@@ -322,9 +327,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             };
             auto commit = [](uint64_t* bar) { if constexpr (PAIR) tc_commit_pair(bar); else tc_commit(bar); };
             for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++local) {
-                const int acc = local % Cfg::ACC_STAGES;
-                const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
-                const uint32_t tmem_acc = tmem_base + acc * BN;
+                const int acc = local & 1;
+                const uint32_t tmem_acc = tmem_base + acc * Cfg::ACC_STRIDE;
+                // the accumulator stage must be free.  OVERLAP: the previous tile's epilogue has read the shared columns
+                // and every epilogue warp has finished reading the tile before it (the last user of this stage);
+                // otherwise: the last user of this stage, two tiles ago, is fully drained
+                if (Cfg::OVERLAP ? local > 0 : true) {
+                    uint64_t* bar = Cfg::OVERLAP ? &acc_empty[0] : &acc_empty[acc];
+                    const uint32_t parity = Cfg::OVERLAP ? ((local - 1) & 1) : (((local >> 1) & 1) ^ 1);
+                    if (!mbar_wait(bar, parity, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                }
                 for (int kt = 0; kt < g.k_tiles; ++kt) {
                     if (!mbar_wait(&full[stage], phase, abort_flag) || !mbar_wait(&sf_full[sfb], sf_phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -333,24 +346,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t sfa_tmem = tmem_base + Cfg::SF_BASE + sfb * Cfg::SF_BUF_COLS;
                     const uint32_t sfb_tmem = sfa_tmem + Cfg::SFA_COLS;
                     const int kblocks = min(4, kb_total - kt * 4);
-                    if (kt == 0) {
-                        // first k-tile: the accumulator comes back from the epilogue in HALVES parts
-#pragma unroll
-                        for (int h = 0; h < Cfg::HALVES; ++h) {
-                            if (!mbar_wait(&acc_empty[acc * Cfg::HALVES + h], acc_phase ^ 1, abort_flag)) { ok = false; break; }
-                            tc_fence_after();
-                            constexpr int NH = BN / Cfg::HALVES;
-                            for (int kb = 0; kb < kblocks; ++kb)
-                                mma(tmem_acc + h * NH, operand_desc(sa + kb * 32), operand_desc(sb + h * NH * 128 + kb * 32),
-                                       Cfg::HALVES == 2 ? idesc_half : idesc_full, kb > 0 ? 1u : 0u, sfa_tmem + kb * 4,
-                                       sfb_tmem + kb * (BN / 32) + h * (NH / 32));
-                        }
-                        if (!ok) break;
-                    } else {
-                        for (int kb = 0; kb < kblocks; ++kb)
-                            mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, 1u,
-                                   sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
-                    }
+                    for (int kb = 0; kb < kblocks; ++kb)
+                        mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, (kt | kb) ? 1u : 0u,
+                            sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
                     commit(&empty[stage]);
                     commit(&sf_empty[sfb]);
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
@@ -422,7 +420,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         const __nv_bfloat162 alpha2 = __float2bfloat162_rn(alpha);
         const bool fast = !g.bias && g.raw_bf16 && !g.out_f32;   // BF16 chain without bias: drain first, store later
-        const int acc_slot_of_half = (Cfg::HALVES == 2) ? half : 0;
         int local = 0;
         bool ok = true;
 
@@ -458,22 +455,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         auto release_acc = [&](uint64_t* bar) { if (PAIR && !leader) mbar_arrive_leader(bar); else mbar_arrive(bar); };
         for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++local) {
             const int tm = (t % g.tiles_m) * Cfg::CTAS + rank, tn = t / g.tiles_m;
-            const int acc = local % Cfg::ACC_STAGES;
-            const uint32_t acc_phase = (local / Cfg::ACC_STAGES) & 1;
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int64_t row = static_cast<int64_t>(tm) * BM + row_in_tile;
             const int tile_row0 = tm * BM + sub * 32;
             const int64_t colbase = static_cast<int64_t>(tn) * BN + half * SHARE;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * BN + half * SHARE;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * Cfg::ACC_STRIDE + half * SHARE;
             const bool rows_live = tile_row0 < g.rows;
+            // OVERLAP: the 96 columns shared with the other stage are this tile's last 96 (stage 0) or first 96
+            // (stage 1).  Their owners (the second / first column half) read them first and release the next tile's
+            // MMAs right after; `rot` rotates the chunk order so that the shared chunks come first.
+            const bool owner = Cfg::OVERLAP && half == (acc ^ 1);
+            const int rot = (Cfg::OVERLAP && acc == 0 && half == 1) ? CHUNKS - Cfg::SHARED_CHUNKS : 0;
+            uint64_t* release_bar = Cfg::OVERLAP ? &acc_empty[0] : &acc_empty[acc];
+            if (Cfg::OVERLAP && !owner) {
+                // the other half arrives at once: having reached this tile it has read all of the previous tile, whose
+                // stage the next tile's MMAs overwrite
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) release_acc(release_bar);
+            }
             if (fast) {
                 uint32_t packed[CHUNKS * 16];
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c) {
                     uint32_t r[32];
-                    tc_ld32(taddr + c * 32, r);
+                    tc_ld32(taddr + ((c + rot) & (CHUNKS - 1)) * 32, r);
                     tc_wait_ld();
+                    if (Cfg::OVERLAP && c == Cfg::SHARED_CHUNKS - 1 && owner) {   // the shared columns are in registers
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) release_acc(release_bar);
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
@@ -481,13 +496,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         packed[c * 16 + j] = *reinterpret_cast<uint32_t*>(&p);
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) release_acc(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);   // accumulator share is in registers
+                if constexpr (!Cfg::OVERLAP) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) release_acc(release_bar);   // accumulator share is in registers
+                }
                 if (rows_live) {
 #pragma unroll
                     for (int c = 0; c < CHUNKS * 2; ++c) {
-                        const int64_t col0 = colbase + c * 16;
+                        const int64_t col0 = colbase + ((c / 2 + rot) & (CHUNKS - 1)) * 32 + (c & 1) * 16;
                         if (col0 < g.cols)
                             emit(make_uint4(packed[c * 8], packed[c * 8 + 1], packed[c * 8 + 2], packed[c * 8 + 3]),
                                  make_uint4(packed[c * 8 + 4], packed[c * 8 + 5], packed[c * 8 + 6], packed[c * 8 + 7]), row, col0, tile_row0, 16);
@@ -496,14 +513,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             } else {
                 const int cols_per_slab = g.out_f32 ? 8 : 16;
 #pragma unroll 1
-                for (int c = 0; c < CHUNKS; ++c) {
+                for (int cc = 0; cc < CHUNKS; ++cc) {
+                    const int c = (cc + rot) & (CHUNKS - 1);
                     uint32_t r[32];
                     tc_ld32(taddr + c * 32, r);
                     tc_wait_ld();
-                    if (c + 1 == CHUNKS) {
+                    if (Cfg::OVERLAP ? (owner && cc == Cfg::SHARED_CHUNKS - 1) : (cc + 1 == CHUNKS)) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) release_acc(&acc_empty[acc * Cfg::HALVES + acc_slot_of_half]);
+                        if (lane == 0) release_acc(release_bar);
                     }
                     if (!rows_live) continue;
                     float v[32];
