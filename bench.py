@@ -166,31 +166,22 @@ def run_quant(args, rank, world, device):
         step(i)
     barrier(world)
     launches = 0
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
-        ev0.record()
-        for i in range(args.steps):
-            step(i)
-        ev1.record()
-        barrier(world)
-    ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps, world, device)
-    timed_launches = launches
+    clk = ClockSampler(torch.cuda.current_device())
+    ms, _ = graph_time(step, args.steps, device, args.profiler_range, clk)   # the K timed steps are one graph replay
+    barrier(world)
+    ms = max_over_ranks(ms, world, device)
+    timed_launches = 6 * args.steps
     bytes_per_step = 4 * C1_BYTES_PER_PASS
     value = world * bytes_per_step / (ms * 1e-3) / 1e9
 
     # dominant kernel alone: the tile quantiser with the tensor scale given (RNE + RHT), rotated inputs
     pts = nat.amax(dev[0])[2:3].clone()
-    reps = max(20, args.steps)
-    for i in range(3):
-        nat.quantize(dev[i % nbuf], signs, 4096, 4096, 0, True, 0, given_scale=pts)
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for i in range(reps):
-        nat.quantize(dev[i % nbuf], signs, 4096, 4096, 0, True, 0, given_scale=pts)
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / reps
+    reps = max(24, args.steps)
+    kernel_ms, _ = graph_time(lambda i: nat.quantize(dev[i % nbuf], signs, 4096, 4096, 0, True, 0, given_scale=pts), reps, device)
+    amax_ms, _ = graph_time(lambda i: nat.amax(dev[i % nbuf]), reps, device)
+    sr_ms, _ = graph_time(lambda i: nat.quantize(dev[i % nbuf], signs, 4096, 4096, nat.Q_SR_PHILOX, True, 0, given_scale=pts), reps, device)
+    deq_in = nat.quantize(dev[0], signs, 4096, 4096, 0, True, 0)
+    deq_ms, _ = graph_time(lambda i: nat.dequantize(deq_in[0], deq_in[1], deq_in[2], 4096, 4096, dtype=torch.bfloat16), reps, device)
     pk = peaks()
     achieved = C1_BYTES_PER_PASS / (kernel_ms * 1e-3) / 1e9
 
@@ -221,12 +212,14 @@ def run_quant(args, rank, world, device):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16->e2m1/ue4m3 (fp32 math)", "data": "synthetic",
         "config": {"workload": "C1: 4096x4096 BF16 N(0,1) + 0.1% x50 outliers per GPU; per step RNE+RHT quantise, dequantise, "
-                               "Philox-SR+RHT quantise (seed 0), dequantise; sign seed 0", "l2": "8 rotated inputs (256 MiB > L2)",
+                               "Philox-SR+RHT quantise (seed 0), dequantise; sign seed 0", "l2": "8 rotated inputs (256 MiB > L2)", "timing": "the timed steps are captured once and replayed as one CUDA graph",
                    "rows_sharded_across_gpus": world},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                      "traffic": None, "kernel": "quant_tile_kernel<bf16,row> (RNE+RHT, scale given)", "kernel_ms": kernel_ms,
                      "peak_source": pk["source"]},
         "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "kernels_us": {"amax": amax_ms * 1e3, "quantize_rne_rht": kernel_ms * 1e3, "quantize_philox_sr_rht": sr_ms * 1e3,
+                       "dequantize_bf16": deq_ms * 1e3},
         "gpu_launches": timed_launches,
         "clocks": clk.summary(),
     }
@@ -261,6 +254,38 @@ def cpu_quant_baseline(base: torch.Tensor, budget_s: float = 12.0):
 # ------------------------------------------------------------------------------------------------
 C2 = dict(tokens=8192, d_in=4096, d_out=4096)
 FP4_NOMINAL_TFLOPS = 9000.0
+
+
+def graph_time(fn, n, device, profiler_range=False, clock=None):
+    """Device time per call of fn(i), i = 0..n-1, with the n calls captured once as a CUDA graph and replayed: kernels of a
+    few tens of microseconds would otherwise be timed at the host's launch rate.  Returns (ms per call, last result)."""
+    from nvfp4_training import _native as nat
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        nat.scratch(device)            # the stream's scratch block exists before capture
+        for i in range(min(n, 3)):
+            fn(i)
+        torch.cuda.synchronize(device)
+        with torch.cuda.graph(graph, stream=side):
+            out = None
+            for i in range(n):
+                out = fn(i)
+    torch.cuda.synchronize(device)
+    graph.replay()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ProfilerRange(profiler_range):
+        if clock is not None:
+            clock.__enter__()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        if clock is not None:
+            clock.__exit__(None, None, None)
+    return e0.elapsed_time(e1) / n, out
 
 
 def time_kernel(fn, reps, profiler_range=False):
@@ -307,7 +332,7 @@ def quant_microbench(device, reps=30):
     from nvfp4_training._backend import quant
     xs = [c1_input(i).to(device) for i in range(8)]
     signs = quant.get_signs(device)
-    ms = time_kernel(lambda i: quant.quantize(xs[i % 8], rht=True, signs=signs), reps)
+    ms, _ = graph_time(lambda i: quant.quantize(xs[i % 8], rht=True, signs=signs), reps, device)
     return ms, C1_BYTES_PER_PASS / (ms * 1e-3) / 1e9
 
 

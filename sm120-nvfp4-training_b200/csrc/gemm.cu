@@ -103,12 +103,21 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when the time limit passed or another role raised the abort flag.
+// try_wait that lets the hardware park the thread until the phase completes or `ns` nanoseconds pass
+__device__ __forceinline__ bool mbar_try_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the time limit passed or another role raised the abort flag.  Waiting threads
+// are parked by the hardware (20 us per attempt) instead of spinning: fourteen warps polling shared memory cost power,
+// and this kernel's speed is set by the clock the power cap allows.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_try_sleep(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; return false; }
     }
