@@ -428,7 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (g.raw_bf16) alpha = bf16_value(bf16_bits(alpha));
         }
         const __nv_bfloat162 alpha2 = __float2bfloat162_rn(alpha);
-        const bool fast = !g.bias && g.raw_bf16 && !g.out_f32;   // BF16 chain without bias: drain first, store later
+        const bool fast = !g.bias && !g.out_f32;   // BF16 output without bias: drain to packed registers first, store later
         int local = 0;
         bool ok = true;
 
@@ -500,8 +500,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                        if (scaled) p = __hmul2(p, alpha2);   // bf16 x bf16 is exact in FP32: one rounding, as in the FP32 chain
+                        __nv_bfloat162 p;
+                        if (g.raw_bf16) {
+                            p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            if (scaled) p = __hmul2(p, alpha2);   // bf16 x bf16 is exact in FP32: one rounding, as in the FP32 chain
+                        } else {   // FP32 chain: acc * alpha in FP32, one rounding to BF16
+                            p = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(r[2 * j]), alpha), __fmul_rn(__uint_as_float(r[2 * j + 1]), alpha));
+                        }
                         packed[c * 16 + j] = *reinterpret_cast<uint32_t*>(&p);
                     }
                 }
