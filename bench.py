@@ -417,7 +417,7 @@ def run_train(args, rank, world, device):
         "tokens_per_s_per_gpu": tokens / (ms * 1e-3), "train_peak_GiB": peak_gib, "loss": losses[0],
         "linear_tflops_in_step": linear_flops / (ms * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak, "traffic": None,
-                     "kernel": f"gemm_kernel<256> fprop+dgrad+wgrad of a {cfg['dim']}x{cfg['ffn']} layer at {tokens} tokens",
+                     "kernel": f"gemm_kernel<256, paired CTAs> fprop+dgrad+wgrad of a {cfg['dim']}x{cfg['ffn']} layer at {tokens} tokens",
                      "kernel_ms": gemm_ms, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)", "frac_of_nominal_9PF": gemm_tf / FP4_NOMINAL_TFLOPS},
         "kernels": {"c2_linear_gemm_tflops": c2_tf, "c2_ms": c2_ms, "c1_quantize_GBps": q_gbs, "c1_quantize_ms": q_ms,
                     "c1_frac_of_hbm": q_gbs / pk["hbm_gbs"]},
@@ -492,7 +492,7 @@ def run_gemm(args, rank, world, device):
             "config": {"workload": "C2: fprop, dgrad, wgrad GEMMs of a 4096x4096 layer at 8192 tokens per GPU on pre-quantised operands "
                                    "(token rows sharded across GPUs, no collective)", "l2": "3 rotated operand sets (~450 MB > L2)"},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf / fp4_peak, "traffic": None,
-                         "kernel": "gemm_kernel<256>", "kernel_ms": ms / 3, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)",
+                         "kernel": "gemm_kernel<256, paired CTAs>", "kernel_ms": ms / 3, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)",
                          "frac_of_nominal_9PF": tf / FP4_NOMINAL_TFLOPS},
             "gpu_launches": 3 * args.steps, "clocks": clk.summary()}
 
