@@ -99,3 +99,31 @@ def test_gemm_argument_errors(native):
         native.gemm(z[:100], s, None, z, s, None, rows=100, cols=128)
     with pytest.raises(ValueError):
         native.gemm(z, s, None, z, s, None, rows=129, cols=128)
+
+
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("m,n,k,rows,cols", [(256, 512, 128, 256, 512), (512, 256, 1024, 500, 250), (256, 256, 384, 255, 129),
+                                             (4096, 4096, 256, 4096, 4096), (2048, 4096, 640, 2048, 4090)])
+@pytest.mark.parametrize("mode", ["bf16", "bf16_bias", "fp32_bias", "fp32_alpha_bf16"])
+def test_gemm_paired_and_single_forms_agree_with_the_oracle(native, pair, m, n, k, rows, cols, mode):
+    """Shapes whose M and N are multiples of 256 run on clusters of two CTAs unless told otherwise; both forms must give
+    the oracle's bits in every epilogue (fast BF16, bias chain, FP32 output, FP32 alpha), with cropped and unaligned
+    outputs, one-k-tile contractions and several tiles per CTA (the two overlapping accumulator stages alternate)."""
+    a, b = _operands(native, m, n, k, seed=3 * m + n + k)
+    out_dtype = torch.float32 if mode == "fp32_bias" else torch.bfloat16
+    raw_bf16 = mode != "fp32_alpha_bf16"
+    bias = None
+    if mode.endswith("bias"):
+        bias = (torch.randn(cols, generator=torch.Generator().manual_seed(5)) * 0.5).to(out_dtype)
+    out = native.gemm(a[0], a[1], a[2], b[0], b[1], b[2], rows=rows, cols=cols, out_dtype=out_dtype, raw_bf16=raw_bf16,
+                      bias=None if bias is None else bias.cuda(), pair=pair)
+    native.check_status()
+    assert out.shape == (rows, cols)
+    pa = (a[0].cpu().numpy(), a[1].cpu().numpy(), float(a[2].item()))
+    pb = (b[0].cpu().numpy(), b[1].cpu().numpy(), float(b[2].item()))
+    want = O.matmul_packed(pa, pb, rows, cols, raw_bf16=raw_bf16, out_bf16=out_dtype == torch.bfloat16,
+                           bias=None if bias is None else bias.float().numpy())
+    got = out.float().cpu().numpy()
+    step = np.abs(want) * 2.0 ** -7 + 1e-12
+    assert (np.abs(got - want) <= 1.01 * step).all()
+    assert (got == want).mean() > 0.98
