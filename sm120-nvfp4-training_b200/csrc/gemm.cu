@@ -52,19 +52,21 @@ template <int BN, bool PAIR> struct GemmCfg {
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES;
     static constexpr int STAGES = PAIR ? 5 : (BN == 256) ? 4 : 6;
     // Two accumulator stages.  Two 256-column accumulators and the scale buffers do not fit the 512 columns of tensor
-    // memory, so with BN = 256 the stages OVERLAP by 96 columns: stage 0 = columns [0, 256), stage 1 = [160, 416),
-    // two scale buffers of 48 columns behind them.  The epilogue reads the shared 96 columns first (the last 96 of a
-    // stage-0 tile, the first 96 of a stage-1 tile) and only that part gates the next tile's MMAs; the rest of the
-    // drain and all stores run under the next mainloop.
+    // memory, so with BN = 256 the stages OVERLAP by 32 columns: stage 0 = columns [0, 256), stage 1 = [224, 480), the
+    // scale buffers behind them.  The epilogue reads the shared 32 columns first (the last 32 of a stage-0 tile, the
+    // first 32 of a stage-1 tile), 16 per warp of a sub-partition, and only that read gates the next tile's MMAs; the
+    // rest of the drain and all stores run under the next mainloop.
+    // The scale buffers hold one k-block (one MMA) each and alternate: the copy for k-block i + 1 writes one buffer
+    // while the MMA of k-block i reads the other (two buffers measured within 1 % of four).
     static constexpr bool OVERLAP = BN == 256;
     static constexpr int ACC_STAGES = 2;
-    static constexpr int ACC_STRIDE = OVERLAP ? 160 : BN;
-    static constexpr int SHARED_CHUNKS = OVERLAP ? (BN - ACC_STRIDE) / 32 : 0;   // 32-column chunks both stages use
-    static constexpr int SFA_COLS = 16;             // 4 k-blocks x 4 columns
-    static constexpr int SFB_COLS = 4 * (BN / 32);  // 4 k-blocks x BN/32 columns
+    static constexpr int ACC_STRIDE = OVERLAP ? 224 : BN;
+    static constexpr int SHARED_COLS = OVERLAP ? BN - ACC_STRIDE : 0;   // columns both stages use
+    static constexpr int SFA_COLS = 4;              // one k-block: 128 rows x 4 scales
+    static constexpr int SFB_COLS = BN / 32;
     static constexpr int SF_BUF_COLS = SFA_COLS + SFB_COLS;
-    static constexpr int SF_BASE = ACC_STRIDE + BN;                     // 416 or 256
-    static constexpr int SF_BUFS = OVERLAP ? 2 : 3;                     // scale buffers, one k-tile each
+    static constexpr int SF_BASE = ACC_STRIDE + BN;                     // 480 or 256
+    static constexpr int SF_BUFS = 2;
     static constexpr int TMEM_COLS = 512;
     static constexpr int EPI_BYTES = EPI_WARPS * EPI_SLAB_BYTES;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * ACC_STAGES;
@@ -182,17 +184,7 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
@@ -371,26 +363,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t sb = sa + A_STAGE_BYTES;
                     const uint32_t ssfa = sb + Cfg::B_STAGE_BYTES;
                     const uint32_t ssfb = ssfa + Cfg::SFA_STAGE_BYTES;
-                    const uint32_t sfa_tmem = tmem_base + Cfg::SF_BASE + sfb * Cfg::SF_BUF_COLS;
-                    const uint32_t sfb_tmem = sfa_tmem + Cfg::SFA_COLS;
                     const int kblocks = min(4, kb_total - kt * 4);
                     if (elect_one()) {
-                        // the copies queue behind the MMAs that still read this scale buffer (issued SF_BUFS k-tiles ago);
                         // each k-block's copies sit directly before its MMA (faster than all twelve up front, and than
-                        // copying one k-tile ahead: 5.16 against 4.79 and 4.85 PFLOP/s at 8192^3)
+                        // copying one k-tile ahead: 5.16 against 4.79 and 4.85 PFLOP/s at 8192^3); a copy queues behind
+                        // the MMA that still reads its scale buffer (issued SF_BUFS k-blocks ago)
                         for (int kb = 0; kb < kblocks; ++kb) {
-                            copy_sf(sfa_tmem + kb * 4, scale_desc(ssfa + kb * SF_BLOCK));
+                            const uint32_t sfa_tmem = tmem_base + Cfg::SF_BASE + (sfb ^ (kb & 1)) * Cfg::SF_BUF_COLS;
+                            const uint32_t sfb_tmem = sfa_tmem + Cfg::SFA_COLS;
+                            copy_sf(sfa_tmem, scale_desc(ssfa + kb * SF_BLOCK));
 #pragma unroll
                             for (int nb = 0; nb < BN / 128; ++nb)
-                                copy_sf(sfb_tmem + kb * (BN / 32) + nb * 4, scale_desc(ssfb + (nb * 4 + kb) * SF_BLOCK));
+                                copy_sf(sfb_tmem + nb * 4, scale_desc(ssfb + (nb * 4 + kb) * SF_BLOCK));
                             mma(tmem_acc, operand_desc(sa + kb * 32), operand_desc(sb + kb * 32), idesc_full, (kt | kb) ? 1u : 0u,
-                                sfa_tmem + kb * 4, sfb_tmem + kb * (BN / 32));
+                                sfa_tmem, sfb_tmem);
                         }
                         commit(&empty[stage]);
                     }
                     __syncwarp();
+                    sfb ^= kblocks & 1;   // every lane keeps the buffer parity: the elected lane need not stay the same
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
-                    if (++sfb == Cfg::SF_BUFS) sfb = 0;
                 }
                 if (ok && elect_one()) commit(&acc_full[acc]);
                 __syncwarp();
@@ -399,9 +391,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int sub = warp & 3;                    // TMEM sub-partition this warp may read
-        const int half = (warp - FIRST_EPI_WARP) >> 2;            // which half of the tile's columns this warp drains
-        constexpr int SHARE = BN / 2;                // columns per warp
-        constexpr int CHUNKS = SHARE / 32;           // tcgen05.ld.x32 loads per share
+        const int half = (warp - FIRST_EPI_WARP) >> 2;   // the two warps of a sub-partition share the tile's columns
+        constexpr int UNITS = BN / 32;               // 16-column units per warp
         const int row_in_tile = sub * 32 + lane;
         uint8_t* slab = epi_smem + (warp - FIRST_EPI_WARP) * EPI_SLAB_BYTES;
         float alpha = 1.f;
@@ -453,36 +444,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tc_fence_after();
             const int64_t row = static_cast<int64_t>(tm) * BM + row_in_tile;
             const int tile_row0 = tm * BM + sub * 32;
-            const int64_t colbase = static_cast<int64_t>(tn) * BN + half * SHARE;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * Cfg::ACC_STRIDE + half * SHARE;
+            const int64_t colbase = static_cast<int64_t>(tn) * BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + acc * Cfg::ACC_STRIDE;
             const bool rows_live = tile_row0 < g.rows;
-            // OVERLAP: the 96 columns shared with the other stage are this tile's last 96 (stage 0) or first 96
-            // (stage 1).  Their owners (the second / first column half) read them first and release the next tile's
-            // MMAs right after; `rot` rotates the chunk order so that the shared chunks come first.
-            const bool owner = Cfg::OVERLAP && half == (acc ^ 1);
-            const int rot = (Cfg::OVERLAP && acc == 0 && half == 1) ? CHUNKS - Cfg::SHARED_CHUNKS : 0;
+            // Which 16-column unit of the tile this warp handles i-th.  OVERLAP: the two units both stages use (the last
+            // two of a stage-0 tile, the first two of a stage-1 tile) come first, one per warp of the sub-partition;
+            // the next tile's MMAs are released as soon as every warp has read its shared unit.  The other fourteen
+            // units are split seven / seven and drained (and stored) under the next mainloop.
+            constexpr int SHARED_UNITS = Cfg::SHARED_COLS / 16;                      // 2 or 0
+            constexpr int OWN_UNITS = (BN / 16 - SHARED_UNITS) / 2;                  // 7 or UNITS
+            auto unit_of = [&](int i) -> int {
+                if constexpr (!Cfg::OVERLAP) return half * UNITS + i;
+                else if (i == 0) return acc == 0 ? BN / 16 - SHARED_UNITS + half : half;
+                else return (acc == 0 ? 0 : SHARED_UNITS) + half * OWN_UNITS + (i - 1);
+            };
             uint64_t* release_bar = Cfg::OVERLAP ? &acc_empty[0] : &acc_empty[acc];
-            if (Cfg::OVERLAP && !owner) {
-                // the other half arrives at once: having reached this tile it has read all of the previous tile, whose
-                // stage the next tile's MMAs overwrite
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) release_acc(release_bar);
-            }
             if (fast) {
-                uint32_t packed[CHUNKS * 16];
+                uint32_t packed[UNITS * 8];
 #pragma unroll
-                for (int c = 0; c < CHUNKS; ++c) {
-                    uint32_t r[32];
-                    tc_ld32(taddr + ((c + rot) & (CHUNKS - 1)) * 32, r);
+                for (int i = 0; i < UNITS; ++i) {
+                    uint32_t r[16];
+                    tc_ld16(taddr + unit_of(i) * 16, r);
                     tc_wait_ld();
-                    if (Cfg::OVERLAP && c == Cfg::SHARED_CHUNKS - 1 && owner) {   // the shared columns are in registers
+                    if (Cfg::OVERLAP && i == 0) {   // the shared unit is in registers
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) release_acc(release_bar);
                     }
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         __nv_bfloat162 p;
                         if (g.raw_bf16) {
                             p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
@@ -490,7 +480,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         } else {   // FP32 chain: acc * alpha in FP32, one rounding to BF16
                             p = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(r[2 * j]), alpha), __fmul_rn(__uint_as_float(r[2 * j + 1]), alpha));
                         }
-                        packed[c * 16 + j] = *reinterpret_cast<uint32_t*>(&p);
+                        packed[i * 8 + j] = *reinterpret_cast<uint32_t*>(&p);
                     }
                 }
                 if constexpr (!Cfg::OVERLAP) {
@@ -500,31 +490,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 if (rows_live) {
 #pragma unroll
-                    for (int c = 0; c < CHUNKS * 2; ++c) {
-                        const int64_t col0 = colbase + ((c / 2 + rot) & (CHUNKS - 1)) * 32 + (c & 1) * 16;
+                    for (int i = 0; i < UNITS; ++i) {
+                        const int64_t col0 = colbase + unit_of(i) * 16;
                         if (col0 < g.cols)
-                            emit(make_uint4(packed[c * 8], packed[c * 8 + 1], packed[c * 8 + 2], packed[c * 8 + 3]),
-                                 make_uint4(packed[c * 8 + 4], packed[c * 8 + 5], packed[c * 8 + 6], packed[c * 8 + 7]), row, col0, tile_row0, 16);
+                            emit(make_uint4(packed[i * 8], packed[i * 8 + 1], packed[i * 8 + 2], packed[i * 8 + 3]),
+                                 make_uint4(packed[i * 8 + 4], packed[i * 8 + 5], packed[i * 8 + 6], packed[i * 8 + 7]), row, col0, tile_row0, 16);
                     }
                 }
             } else {
                 const int cols_per_slab = g.out_f32 ? 8 : 16;
 #pragma unroll 1
-                for (int cc = 0; cc < CHUNKS; ++cc) {
-                    const int c = (cc + rot) & (CHUNKS - 1);
-                    uint32_t r[32];
-                    tc_ld32(taddr + c * 32, r);
+                for (int i = 0; i < UNITS; ++i) {
+                    const int64_t ucol = colbase + unit_of(i) * 16;
+                    uint32_t r[16];
+                    tc_ld16(taddr + unit_of(i) * 16, r);
                     tc_wait_ld();
-                    if (Cfg::OVERLAP ? (owner && cc == Cfg::SHARED_CHUNKS - 1) : (cc + 1 == CHUNKS)) {
+                    if (Cfg::OVERLAP ? i == 0 : i + 1 == UNITS) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) release_acc(release_bar);
                     }
                     if (!rows_live) continue;
-                    float v[32];
+                    float v[16];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int64_t col = colbase + c * 32 + j;
+                    for (int j = 0; j < 16; ++j) {
+                        const int64_t col = ucol + j;
                         float x = __uint_as_float(r[j]);
                         if (g.raw_bf16) x = bf16_value(bf16_bits(x));
                         if (scaled) {
@@ -541,10 +531,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         v[j] = x;
                     }
 #pragma unroll
-                    for (int sl = 0; sl < 4; ++sl) {          // up to four 32-byte slabs per 32 columns
-                        if (sl * cols_per_slab >= 32) break;
+                    for (int sl = 0; sl < 2; ++sl) {          // one 32-byte slab of BF16 or two of FP32 per unit
+                        if (sl * cols_per_slab >= 16) break;
                         const int j0 = sl * cols_per_slab;
-                        const int64_t col0 = colbase + c * 32 + j0;
+                        const int64_t col0 = ucol + j0;
                         if (col0 >= g.cols) continue;
                         uint4 q0, q1;
                         if (g.out_f32) {
@@ -553,7 +543,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         } else {
                             uint32_t w[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) w[j] = bf16_bits(v[j0 + 2 * j]) | (uint32_t(bf16_bits(v[j0 + 2 * j + 1])) << 16);
+                            for (int j = 0; j < 8; ++j) w[j] = bf16_bits(v[2 * j]) | (uint32_t(bf16_bits(v[2 * j + 1])) << 16);
                             q0 = make_uint4(w[0], w[1], w[2], w[3]); q1 = make_uint4(w[4], w[5], w[6], w[7]);
                         }
                         emit(q0, q1, row, col0, tile_row0, cols_per_slab);
