@@ -83,6 +83,44 @@ class AdamW(torch.optim.Optimizer):
     def _grad_mul(self):
         return 1.0 if self.reducer is None else self.reducer.grad_scale
 
+    # ---- updates overlapped with the rest of backward (captured steps) ------------------------------------
+    #: Under capture, parameter updates are recorded on a second stream that forks after the parameter's gradient is
+    #: complete and joins at the end of backward.  The AdamW kernel is bound by integer / FP32 instruction issue and
+    #: the GEMMs, attention and copies around it are not, so the graph may run them on the same SMs at once.  Results
+    #: do not change: same kernels on the same values, only their placement in the graph.
+    overlap_updates = True
+
+    def update_stream(self, device):
+        """The stream captured updates are recorded on (created on first use, with its amax scratch)."""
+        streams = self.__dict__.setdefault("_update_streams", {})
+        key = torch.device(device).index
+        if key not in streams:
+            streams[key] = torch.cuda.Stream(device=device)
+            with torch.cuda.stream(streams[key]):
+                nat.scratch(torch.device(device))
+        return streams[key]
+
+    def _update_overlapped(self, p, group, pack):
+        if not self.overlap_updates or not torch.cuda.is_current_stream_capturing():
+            return self._update_param(p, group, pack)
+        side, main = self.update_stream(p.device), torch.cuda.current_stream(p.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            self._update_param(p, group, pack)
+        # gradients were allocated on the capturing stream and die with this call: keep their memory out of reuse
+        # until the update that reads them has run
+        for t in (*(pack or ()), p.grad):
+            if torch.is_tensor(t) and t.is_cuda:
+                t.record_stream(side)
+        published = getattr(p, "_v4_scale", None)
+        if published is not None and published[2] == side.cuda_stream:
+            p._v4_scale = (published[0], published[1], main.cuda_stream, published[3])
+        self.__dict__.setdefault("_forked", set()).add(torch.device(p.device).index)
+
+    def _join_updates(self):
+        for index in self.__dict__.pop("_forked", ()):
+            torch.cuda.current_stream(index).wait_stream(self._update_streams[index])
+
     def _publish_scale(self, p, scale):
         p._v4_scale = (p._version, p.data_ptr(), torch.cuda.current_stream(p.device).cuda_stream, scale)
 
@@ -185,10 +223,10 @@ class AdamW(torch.optim.Optimizer):
         grad = held.pop(p, None)
         if pack is not None and pack[1] is None and pack[2] is None and grad is not None and pack[0] is grad:
             p.grad = grad                     # dense leaf gradient: the ordinary path reads p.grad
-            self._update_param(p, group, None)
+            self._update_overlapped(p, group, None)
             p.grad = None
         else:
-            self._update_param(p, group, pack)
+            self._update_overlapped(p, group, pack)
 
     def capture_streaming_backward(self, loss):
         """Record parameter-local updates once, as soon as each parameter's gradient is complete, inside backward
@@ -212,7 +250,7 @@ class AdamW(torch.optim.Optimizer):
                     raise RuntimeError("Unexpected leaf gradient during capture")
                 with torch.no_grad():
                     if reducer is None:
-                        self._update_param(p, group, pack)
+                        self._update_overlapped(p, group, pack)
                         p.grad = None
                     else:
                         held[p] = p.grad          # keep the leaf gradient alive until its collective is consumed
@@ -239,6 +277,7 @@ class AdamW(torch.optim.Optimizer):
             if pending or len(completed) != len(params):
                 raise RuntimeError("Every parameter must receive its complete gradient once")
         finally:
+            self._join_updates()
             for handle in handles:
                 handle.remove()
             for p in owners:

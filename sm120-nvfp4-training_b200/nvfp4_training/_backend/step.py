@@ -67,7 +67,9 @@ class StaticStep:
                     self.scales[p] = cached[3]
         optimizer.zero_grad(set_to_none=True)
         self.graph = torch.cuda.CUDAGraph()
-        capture_stream = torch.cuda.Stream(device=self.device)
+        # captured kernel nodes inherit the stream's priority: the main line of the step is placed before the overlapped
+        # optimizer updates, which fill what it leaves free
+        capture_stream = torch.cuda.Stream(device=self.device, priority=-1 if stream_updates and optimizer.overlap_updates else 0)
         capture_stream.wait_stream(self.stream)
         if from_start:
             # library handles (cuBLAS for attention / loss math) are created lazily and may not allocate under capture
@@ -80,6 +82,8 @@ class StaticStep:
             from .. import _native
             _native.scratch(self.device)          # per-stream amax scratch must exist before capture
             _native.status_word(self.device)
+        if stream_updates and optimizer.overlap_updates:
+            optimizer.update_stream(self.device).synchronize()   # the second stream and its scratch exist before capture
         capture_stream.synchronize()
         try:
             for p in owners:
