@@ -100,12 +100,23 @@ class AdamW(torch.optim.Optimizer):
                 nat.scratch(torch.device(device))
         return streams[key]
 
-    def _update_overlapped(self, p, group, pack):
-        if not self.overlap_updates or not torch.cuda.is_current_stream_capturing():
+    def _overlapping(self):
+        return self.overlap_updates and torch.cuda.is_current_stream_capturing()
+
+    def _update_overlapped(self, p, group, pack, work=None):
+        """work: the all-reduce of this gradient, still to be waited for.  The update stream waits for it (the
+        collective itself was ordered after the gradient's producer when it was launched); without a collective the
+        update stream forks from the calling stream here."""
+        if not self._overlapping():
+            if work is not None:
+                work.wait()
             return self._update_param(p, group, pack)
         side, main = self.update_stream(p.device), torch.cuda.current_stream(p.device)
-        side.wait_stream(main)
+        if work is None or not self.__dict__.get("_forked"):
+            side.wait_stream(main)
         with torch.cuda.stream(side):
+            if work is not None:
+                work.wait()
             self._update_param(p, group, pack)
         # gradients were allocated on the capturing stream and die with this call: keep their memory out of reuse
         # until the update that reads them has run
@@ -218,15 +229,15 @@ class AdamW(torch.optim.Optimizer):
             for p, g in active:
                 self._update_param(p, g, pending.pop(p, None))
 
-    def _finish_streamed(self, p, group, pack, held):
+    def _finish_streamed(self, p, group, pack, held, work=None):
         """Update p from a gradient whose all-reduce has completed (stream-wise)."""
         grad = held.pop(p, None)
         if pack is not None and pack[1] is None and pack[2] is None and grad is not None and pack[0] is grad:
             p.grad = grad                     # dense leaf gradient: the ordinary path reads p.grad
-            self._update_overlapped(p, group, None)
+            self._update_overlapped(p, group, None, work)
             p.grad = None
         else:
-            self._update_overlapped(p, group, pack)
+            self._update_overlapped(p, group, pack, work)
 
     def capture_streaming_backward(self, loss):
         """Record parameter-local updates once, as soon as each parameter's gradient is complete, inside backward
@@ -255,8 +266,9 @@ class AdamW(torch.optim.Optimizer):
                     else:
                         held[p] = p.grad          # keep the leaf gradient alive until its collective is consumed
                         p.grad = None
-                        for q, gq, packq in reducer.submit(p, group, pack if pack is not None else (held[p], None, None)):
-                            self._finish_streamed(q, gq, packq, held)
+                        for q, gq, packq, work in reducer.submit(p, group, pack if pack is not None else (held[p], None, None),
+                                                                 wait=False):
+                            self._finish_streamed(q, gq, packq, held, work)
                 completed.add(p)
             return update
         try:
@@ -272,8 +284,8 @@ class AdamW(torch.optim.Optimizer):
             loss.backward()
             if reducer is not None:
                 with torch.no_grad():
-                    for q, gq, packq in reducer.drain():
-                        self._finish_streamed(q, gq, packq, held)
+                    for q, gq, packq, work in reducer.drain(wait=False):
+                        self._finish_streamed(q, gq, packq, held, work)
             if pending or len(completed) != len(params):
                 raise RuntimeError("Every parameter must receive its complete gradient once")
         finally:

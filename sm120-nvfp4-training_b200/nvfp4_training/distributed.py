@@ -74,26 +74,29 @@ class GradientReducer:
             self._works.clear()
 
     # ---- streaming protocol (updates inside backward, eager or captured) ------------------------------
-    def submit(self, p, group, pack):
+    def submit(self, p, group, pack, wait=True):
         """Start the collective for p's gradient and return the (param, group, pack) items whose collectives have had
-        `depth` later submissions to overlap with; those are safe to update now (after a stream-level wait)."""
+        `depth` later submissions to overlap with; those are safe to update now (after a stream-level wait).
+        wait=False leaves that wait to the caller, who gets (param, group, pack, work) and may place it on the stream
+        its update runs on, so that the calling stream never waits for a collective."""
         tensor = pack[0] if pack is not None else p.grad
         work = dist.all_reduce(tensor, group=self.group, async_op=True)
         self.launched.append(p)
         self._queue.append((p, group, pack, work))
-        ready = []
-        while len(self._queue) > self.depth:
-            q, g, k, w = self._queue.popleft()
-            w.wait()
-            ready.append((q, g, k))
-        return ready
+        return self._pop(self.depth, wait)
 
-    def drain(self):
+    def drain(self, wait=True):
+        return self._pop(0, wait)
+
+    def _pop(self, keep, wait):
         ready = []
-        while self._queue:
+        while len(self._queue) > keep:
             q, g, k, w = self._queue.popleft()
-            w.wait()
-            ready.append((q, g, k))
+            if wait:
+                w.wait()
+                ready.append((q, g, k))
+            else:
+                ready.append((q, g, k, w))
         return ready
 
 
@@ -104,6 +107,11 @@ def enable_data_parallel(model, process_group=None, *, bucket_mb=None, depth=2):
         raise RuntimeError("torch.distributed must be initialised before enable_data_parallel")
     opt = model.nvfp4_optimizer
     params = [p for g in opt.param_groups for p in g["params"]]
+    if process_group is None and dist.get_backend() == "nccl" and getattr(opt, "overlap_updates", False):
+        # A captured step runs its main line on a high-priority stream and the optimizer updates below it; the
+        # collectives belong with the main line, or they would only run in its gaps and pile up behind backward.
+        options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        process_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend="nccl", pg_options=options)
     reducer = GradientReducer(params, process_group, depth=depth)
     opt.reducer = reducer
     from ._backend import quant
