@@ -86,22 +86,21 @@ __device__ __forceinline__ float uniform24(uint32_t bits) {
 }
 
 // ---- E2M1 stochastic level choice ---------------------------------------------------------------
-// x in [0, 6], h24 = 24 random bits (u = h24 * 2^-24).  Level spacing is 1/2 below 2, 1 below 4, 2 above, i.e.
-// 2^(e-1) with e the exponent of max(x, 1).  With xs = x / spacing (exact), the lower level is floor(xs) steps from
-// zero and the round-up probability is frac(xs); "u < p" is tested as "h24 < p * 2^24".  Everything is exact
-// arithmetic on the same real numbers as (x - lo) / (hi - lo) < u, so the result is bit-identical, and no
-// conversion instruction is needed: floor comes from a round-down add of 2^23, float(h24) from mantissa injection.
-__device__ __forceinline__ uint32_t sr_code(float x, uint32_t h24) {
-    const uint32_t e_biased = __float_as_uint(fmaxf(x, 1.0f)) >> 23;              // 127, 128 or 129
-    const float rw = __uint_as_float((255u - e_biased) << 23);                    // 2, 1 or 1/2
-    const float xs = __fmul_rn(x, rw);
-    const float tm = __fadd_rd(xs, 8388608.f);                                    // 2^23 + floor(xs)
-    const uint32_t steps = __float_as_uint(tm) & 7u;
-    const float p24 = __fmul_rn(__fsub_rn(xs, __fsub_rn(tm, 8388608.f)), 16777216.f);
-    const float hf = __fadd_rn(__fsub_rn(__uint_as_float(0x4B000000u | (h24 & 0x7FFFFFu)), 8388608.f),
-                               __uint_as_float((h24 >> 23) * 0x4B000000u));
-    return steps + 2u * (e_biased - 127u) + static_cast<uint32_t>(hf < p24);
+// x in [0, 6], 24 random bits h24 (u = h24 * 2^-24).  Level spacing is 1/2 below 2, 1 below 4, 2 above, i.e. 2^(e-1)
+// with e the exponent of max(x, 1).  With xs = x / spacing (exact), the lower level is floor(xs) steps from zero and
+// the round-up probability is frac(xs); "u < p" is h24 < frac(xs) * 2^24, which for the integer h24 is
+// h24 < C := ceil(frac(xs) * 2^24).  All of it is one integer sum: with F = ceil(xs * 2^24) = floor(xs) * 2^24 + C,
+// F + (2^24 - 1 - h24) has floor(xs) + [h24 < C] in the bits above 24, and adding (e - 127) << 25 puts the level's
+// base (0, 2 or 4 steps) there too.  Exact arithmetic on the same real numbers as (x - lo) / (hi - lo) < u, hence
+// bit-identical to it.  The caller passes nh = 2^24 - 1 - h24, or a value `bias` short of it.
+__device__ __forceinline__ uint32_t sr_code_n(float x, uint32_t nh, uint32_t bias = 0u) {
+    const uint32_t ex = __float_as_uint(fmaxf(x, 1.0f)) & 0x7F800000u;            // exponent field 127, 128 or 129
+    const float rw24 = __uint_as_float(0x8B800000u - ex);                         // 2^24 / spacing = 2^25, 2^24, 2^23
+    const uint32_t f = static_cast<uint32_t>(__float2int_ru(__fmul_rn(x, rw24)));  // < 2^27; the product is exact
+    const uint32_t base = (ex << 2) + 0x02000000u + bias;                         // (e - 127) << 25 modulo 2^32
+    return (f + nh + base) >> 24;
 }
+__device__ __forceinline__ uint32_t sr_code(float x, uint32_t h24) { return sr_code_n(x, h24 ^ 0xFFFFFFu); }
 
 // ---- scale-factor swizzle (32 x 4 x 4 atom inside 128-row x 4-group blocks) ------------------------
 __host__ __device__ __forceinline__ int64_t scale_offset(int64_t row, int64_t group_col, int64_t groups_per_row) {

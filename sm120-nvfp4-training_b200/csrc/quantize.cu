@@ -209,13 +209,15 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
 #pragma unroll
         for (int l = 0; l < 16; ++l) {
             const float q = __fmul_rn(v[l], mul);
-            uint32_t h24;
-            if constexpr (SR == SR_HASH) h24 = shr_mul(hash32_mixed(hbase + l), 1u << 24);
-            else h24 = ((rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8;   // 16-bit uniform on the 24-bit grid
+            // complement of the 24 random bits (the level choice adds it); Philox: 16-bit uniform on the 24-bit grid,
+            // whose complement is (~r16 << 8) | 0xff
+            uint32_t nh, bias = 0u;
+            if constexpr (SR == SR_HASH) nh = shr_mul(~hash32_mixed(hbase + l), 1u << 24);
+            else { nh = ((~rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8; bias = 0xffu; }
             // sign bit set iff q < 0 (so -0 encodes as +0): q < 0  <=>  sign bit set and magnitude non-zero
             const uint32_t qb = __float_as_uint(q);
             const uint32_t neg = (qb > 0x80000000u) ? 8u : 0u;
-            codes[l] = sr_code(fminf(fabsf(q), 6.f), h24) | neg;
+            codes[l] = sr_code_n(fminf(fabsf(q), 6.f), nh, bias) | neg;
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
