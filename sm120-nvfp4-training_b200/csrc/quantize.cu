@@ -150,13 +150,18 @@ __device__ __forceinline__ void hadamard16_unscaled(float (&v)[16], const float 
         v[2 * p] = __fmaf_rn(b, sb, a);
         v[2 * p + 1] = __fmaf_rn(b, -sb, a);
     }
+    // stages 2, 4, 8 pair whole (even, odd) couples: two-wide FP32 instructions, each half one IEEE rounding as before
+    // (x - y is fma(y, -1, x): the product is exact)
+    const float2 minus = make_float2(-1.f, -1.f);
 #pragma unroll
     for (int d = 2; d < 16; d <<= 1) {
-        float t[16];
 #pragma unroll
-        for (int l = 0; l < 16; ++l) t[l] = (l & d) ? __fsub_rn(v[l ^ d], v[l]) : __fadd_rn(v[l], v[l ^ d]);
-#pragma unroll
-        for (int l = 0; l < 16; ++l) v[l] = t[l];
+        for (int l = 0; l < 16; l += 2) {
+            if (l & d) continue;
+            const float2 lo = make_float2(v[l], v[l + 1]), hi = make_float2(v[l ^ d], v[(l ^ d) + 1]);
+            const float2 sum = __fadd2_rn(lo, hi), dif = __ffma2_rn(hi, minus, lo);
+            v[l] = sum.x; v[l + 1] = sum.y; v[l ^ d] = dif.x; v[(l ^ d) + 1] = dif.y;
+        }
     }
 }
 
@@ -179,13 +184,19 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
     scale_byte = e8;
     float mul = __fdiv_rn(inv_pts, e4m3_normal_to_float(e8));
     if (fold) mul = __fmul_rn(mul, 0.25f);
+    float q[16];   // v * mul, two per instruction
+    const float2 mul2 = make_float2(mul, mul);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const float2 t = __fmul2_rn(make_float2(v[2 * p], v[2 * p + 1]), mul2);
+        q[2 * p] = t.x; q[2 * p + 1] = t.y;
+    }
     uint32_t lo = 0, hi = 0;
     if constexpr (SR == SR_NONE) {
         // cvt.rn.satfinite clamps to +-6 by itself
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const float q0 = __fmul_rn(v[2 * b], mul), q1 = __fmul_rn(v[2 * b + 1], mul);
-            const float q2 = __fmul_rn(v[8 + 2 * b], mul), q3 = __fmul_rn(v[8 + 2 * b + 1], mul);
+            const float q0 = q[2 * b], q1 = q[2 * b + 1], q2 = q[8 + 2 * b], q3 = q[8 + 2 * b + 1];
             const float2 p0 = hi_first ? make_float2(q1, q0) : make_float2(q0, q1);
             const float2 p1 = hi_first ? make_float2(q3, q2) : make_float2(q2, q3);
             lo |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p0, __NV_E2M1, cudaRoundNearest)) << (8 * b);
@@ -208,16 +219,16 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
         const uint32_t hbase = seed * 0x9e3779b9u + static_cast<uint32_t>(idx0) + 0x85ebca6bu;
 #pragma unroll
         for (int l = 0; l < 16; ++l) {
-            const float q = __fmul_rn(v[l], mul);
+            const float ql = q[l];
             // complement of the 24 random bits (the level choice adds it); Philox: 16-bit uniform on the 24-bit grid,
             // whose complement is (~r16 << 8) | 0xff
             uint32_t nh, bias = 0u;
             if constexpr (SR == SR_HASH) nh = shr_mul(~hash32_mixed(hbase + l), 1u << 24);
             else { nh = ((~rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8; bias = 0xffu; }
             // sign bit set iff q < 0 (so -0 encodes as +0): q < 0  <=>  sign bit set and magnitude non-zero
-            const uint32_t qb = __float_as_uint(q);
+            const uint32_t qb = __float_as_uint(ql);
             const uint32_t neg = (qb > 0x80000000u) ? 8u : 0u;
-            codes[l] = sr_code_n(fminf(fabsf(q), 6.f), nh, bias) | neg;
+            codes[l] = sr_code_n(fminf(fabsf(ql), 6.f), nh, bias) | neg;
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -286,7 +297,7 @@ __device__ __forceinline__ void load_group_bf16(const void* x, int64_t r, int64_
 }
 
 template <int DT, bool ROW, bool COL, int SR>
-__global__ void __launch_bounds__(256) quant_tile_kernel(const void* __restrict__ x, int64_t rows, int64_t cols,
+__global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restrict__ x, int64_t rows, int64_t cols,
                                                          int64_t rs, int64_t cs, int vec_ok,
                                                          const float* __restrict__ signs,
                                                          const int32_t* __restrict__ seed_base, Orient R, Orient C) {
