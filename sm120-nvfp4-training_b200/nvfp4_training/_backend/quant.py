@@ -24,6 +24,16 @@ _STATS = {"fp4_gemm": 0, "quant": 0, "sr_quant": 0, "rht_quant": 0, "reused_weig
 # gate / up) get identical packings, so the second and third reuse the first's.  The entry keeps its source alive, so
 # no other tensor can appear at the same address while it is valid; the version counter catches in-place edits.
 _LAST_DUAL: dict = {}
+# Tensors made during a graph capture live in the graph's memory pool and die with the graph, so an entry made under
+# capture may not outlive it: the memo works under capture only between remember_in_capture(True) and (False), which
+# the step capture brackets its recording with, and every switch forgets what is held.
+_MEMO_IN_CAPTURE = False
+
+
+def remember_in_capture(on: bool) -> None:
+    global _MEMO_IN_CAPTURE
+    _MEMO_IN_CAPTURE = bool(on)
+    _LAST_DUAL.clear()
 
 
 def sr_flag() -> int:
@@ -124,8 +134,9 @@ def dual(x: torch.Tensor, signs: torch.Tensor, *, sr: bool = False, clock=None, 
     m, n = x.shape
     mp, np_ = round128(m), round128(n)
     key = None
-    if not sr:
-        key = (x.data_ptr(), x._version, tuple(x.shape), x.stride(), x.dtype, signs.data_ptr(), signs._version,
+    capturing = torch.cuda.is_current_stream_capturing()
+    if not sr and (_MEMO_IN_CAPTURE or not capturing):
+        key = (capturing, x.data_ptr(), x._version, tuple(x.shape), x.stride(), x.dtype, signs.data_ptr(), signs._version,
                torch.cuda.current_stream(x.device).cuda_stream)
         hit = _LAST_DUAL.get(x.device)
         if hit is not None and hit[0] == key:

@@ -91,6 +91,7 @@ class StaticStep:
             for p, scale in self.scales.items():
                 p._v5_graph_scale = scale
             optimizer._graph_control = self.ctrl
+            rng.remember_in_capture(True)
             with torch.cuda.graph(self.graph, stream=capture_stream):
                 self.loss = compute(self.x, self.y)
                 if stream_updates:
@@ -101,6 +102,7 @@ class StaticStep:
             if any(optimizer.state[p]['step'] != self.start + 1 for p in self.params):
                 raise RuntimeError("Every owned parameter must participate in the captured step")
         finally:
+            rng.remember_in_capture(False)
             for p in owners:
                 del p._v5_clock
             for p in self.scales:

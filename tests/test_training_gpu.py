@@ -144,3 +144,28 @@ def test_small_decoder_trains():
         last = nv.train_step(model, token_loss, x, y).item()
     assert last < 0.7 * first
     nv.check_finite(model)
+
+
+def test_layers_sharing_an_input_reuse_its_packing_and_edits_invalidate_it():
+    """Round-to-nearest activation pairs are deterministic, so consecutive layers reading one tensor share them; the
+    entry must die with an in-place edit of the source, and stochastic pairs are never shared."""
+    from nvfp4_training._backend import quant
+    signs = quant.get_signs(torch.device("cuda"))
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16, generator=g)
+    quant.reset_stats(0)
+    first = quant.dual(x, signs)
+    again = quant.dual(x.reshape(-1, 384), signs)           # a new view of the same storage
+    assert again[0].data is first[0].data and again[1].data is first[1].data
+    assert quant.stats()["activation_pack_reused"] == 1 and quant.stats()["quant"] == 4
+    x.mul_(2)                                                # version bump
+    fresh = quant.dual(x, signs)
+    assert fresh[0].data is not first[0].data and quant.stats()["activation_pack_reused"] == 1
+    assert not torch.equal(fresh[0].pts, first[0].pts)
+    other = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16, generator=g)
+    assert quant.dual(other, signs)[0].data is not fresh[0].data
+    back = quant.dual(x, signs)                              # only the last pair is remembered
+    assert back[0].data is not fresh[0].data and torch.equal(back[0].data, fresh[0].data)
+    assert torch.equal(back[1].data, fresh[1].data) and torch.equal(back[0].scale, fresh[0].scale)
+    a, b = quant.dual(x, signs, sr=True), quant.dual(x, signs, sr=True)
+    assert a[0].data is not b[0].data and not torch.equal(a[0].data, b[0].data)
