@@ -101,6 +101,25 @@ __device__ __forceinline__ uint32_t sr_code_n(float x, uint32_t nh, uint32_t bia
     return (f + nh + base) >> 24;
 }
 __device__ __forceinline__ uint32_t sr_code(float x, uint32_t h24) { return sr_code_n(x, h24 ^ 0xFFFFFFu); }
+__device__ __forceinline__ uint32_t mad_lo(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+// Signed form: the whole 4-bit code (bit 3 = sign, set iff q < 0) of q clamped to [-6, 6].  Same sum as sr_code_n with
+// the sign added in as 1 << 27; the integer adds, the shifts and the sign extraction are written as multiply-adds so
+// that they run on the FMA pipe, which these kernels leave half idle while the ALU pipe is their limit.  q + 0 turns
+// -0 into +0 (round-to-nearest), after which "q < 0" is the sign bit.
+__device__ __forceinline__ uint32_t sr_code_signed(float q, uint32_t nh, uint32_t bias = 0u) {
+    const float qz = __fadd_rn(q, 0.0f);
+    const uint32_t sgn = shr_mul(__float_as_uint(qz), 2u);
+    const float x = fminf(fabsf(qz), 6.f);
+    const uint32_t ex = __float_as_uint(fmaxf(x, 1.0f)) & 0x7F800000u;
+    const float rw24 = __uint_as_float(mad_lo(ex, 0xFFFFFFFFu, 0x8B800000u));
+    const uint32_t f = static_cast<uint32_t>(__float2int_ru(__fmul_rn(x, rw24)));
+    const uint32_t base = mad_lo(sgn, 0x08000000u, mad_lo(ex, 4u, 0x02000000u + bias));
+    return shr_mul(f + nh + base, 256u);
+}
 
 // ---- scale-factor swizzle (32 x 4 x 4 atom inside 128-row x 4-group blocks) ------------------------
 __host__ __device__ __forceinline__ int64_t scale_offset(int64_t row, int64_t group_col, int64_t groups_per_row) {

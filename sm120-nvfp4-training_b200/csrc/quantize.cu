@@ -225,10 +225,7 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
             uint32_t nh, bias = 0u;
             if constexpr (SR == SR_HASH) nh = shr_mul(~hash32_mixed(hbase + l), 1u << 24);
             else { nh = ((~rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8; bias = 0xffu; }
-            // sign bit set iff q < 0 (so -0 encodes as +0): q < 0  <=>  sign bit set and magnitude non-zero
-            const uint32_t qb = __float_as_uint(ql);
-            const uint32_t neg = (qb > 0x80000000u) ? 8u : 0u;
-            codes[l] = sr_code_n(fminf(fabsf(ql), 6.f), nh, bias) | neg;
+            codes[l] = sr_code_signed(ql, nh, bias);   // sign bit set iff q < 0 (so -0 encodes as +0)
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
