@@ -94,7 +94,9 @@ def make_quant(out: Path):
 
 
 if __name__ == "__main__":
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the reference's src directory> [all|quant|...]")
+    ref_src = sys.argv[1]
     sys.path.insert(0, ref_src)
     which = sys.argv[2] if len(sys.argv) > 2 else "all"
     if which in ("all", "quant"):
