@@ -366,6 +366,7 @@ def run_train(args, rank, world, device):
     warm_attention(model, mb, seq, device)
     torch.cuda.reset_peak_memory_stats()
     graph = nv.capture_step(model, token_loss, x0, y0, steps=total)
+    captured_calls = graph.library_calls   # library calls recorded into the step's graph (>= one kernel each)
     dev_ids = ids.to(device)
     losses = []
     with graph:
@@ -397,8 +398,9 @@ def run_train(args, rank, world, device):
     nv.check_finite(model)
     peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
     n_layers_linear = sum(1 for m in model.modules() if isinstance(m, torch.nn.Linear))
-    # per converted layer and step: 2 amax + 2 dual + 1 weight pair + 3 GEMM + 1 AdamW; plus one AdamW per other parameter
-    kernel_launches = n_layers_linear * 9 + (len(list(model.parameters())) - n_layers_linear)
+    # counted, not derived: every call into the C-ABI library made while the step was captured launches at least one
+    # kernel of this repository (amax, quantisers, GEMMs, AdamW, RoPE, SwiGLU) and is replayed once per step
+    kernel_launches = captured_calls
     pk = peaks()
     gemm_ms, gemm_tf = gemm_microbench(device, tokens, cfg["dim"], cfg["ffn"])
     c2_ms, c2_tf = gemm_microbench(device, C2["tokens"], C2["d_in"], C2["d_out"])

@@ -92,12 +92,14 @@ class StaticStep:
                 p._v5_graph_scale = scale
             optimizer._graph_control = self.ctrl
             rng.remember_in_capture(True)
+            calls = _native.CALLS
             with torch.cuda.graph(self.graph, stream=capture_stream):
                 self.loss = compute(self.x, self.y)
                 if stream_updates:
                     optimizer.capture_streaming_backward(self.loss)
                 else:
                     optimizer.backward_step(self.loss)
+            self.library_calls = _native.CALLS - calls   # C-ABI calls recorded in the graph: one or two kernels each
             self.loss = self.loss.detach()
             if any(optimizer.state[p]['step'] != self.start + 1 for p in self.params):
                 raise RuntimeError("Every owned parameter must participate in the captured step")

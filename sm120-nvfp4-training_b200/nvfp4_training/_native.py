@@ -70,7 +70,12 @@ def lib():
     return _lib
 
 
+CALLS = 0   # kernel-launching library calls made by this process (each launches one or two kernels)
+
+
 def check(code: int) -> None:
+    global CALLS
+    CALLS += 1
     if code:
         message = lib().nvfp4_last_error().decode("utf-8", "replace")
         raise _ERRORS.get(code, RuntimeError)(message)
