@@ -215,7 +215,8 @@ def run_quant(args, rank, world, device):
                                "Philox-SR+RHT quantise (seed 0), dequantise; sign seed 0", "l2": "8 rotated inputs (256 MiB > L2)", "timing": "the timed steps are captured once and replayed as one CUDA graph",
                    "rows_sharded_across_gpus": world},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                     "traffic": None, "kernel": "quant_tile_kernel<bf16,row> (RNE+RHT, scale given)", "kernel_ms": kernel_ms,
+                     "traffic": NCU_TRAFFIC["quant_c1"], "traffic_source": NCU_TRAFFIC_SOURCE["quant_c1"],
+                     "kernel": "quant_tile_kernel<bf16,row> (RNE+RHT, scale given)", "kernel_ms": kernel_ms,
                      "peak_source": pk["source"]},
         "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "kernels_us": {"amax": amax_ms * 1e3, "quantize_rne_rht": kernel_ms * 1e3, "quantize_philox_sr_rht": sr_ms * 1e3,
@@ -254,6 +255,11 @@ def cpu_quant_baseline(base: torch.Tensor, budget_s: float = 12.0):
 # ------------------------------------------------------------------------------------------------
 C2 = dict(tokens=8192, d_in=4096, d_out=4096)
 FP4_NOMINAL_TFLOPS = 9000.0
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures summarised under profiles/
+# (one capture per kernel; outputs still resident in the 126 MB L2 at kernel end are not in them)
+NCU_TRAFFIC = {"gemm_c2": (50.2e6 + 50.6e6 + 42.3e6) / 3, "quant_c1": 33.6e6, "adamw": 293.5e6}
+NCU_TRAFFIC_SOURCE = {"gemm_c2": "profiles/gemm_kernel_c2.md", "quant_c1": "profiles/quant_tile_kernel_c1.md",
+                      "adamw": "profiles/adamw_kernel_balanced.md"}
 
 
 def graph_time(fn, n, device, profiler_range=False, clock=None):
@@ -418,7 +424,10 @@ def run_train(args, rank, world, device):
                    "l2": "per-step working set (weights 7.6 GB + activations) exceeds the 126 MB L2"},
         "tokens_per_s_per_gpu": tokens / (ms * 1e-3), "train_peak_GiB": peak_gib, "loss": losses[0],
         "linear_tflops_in_step": linear_flops / (ms * 1e-3) / 1e12,
-        "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak, "traffic": None,
+        "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak,
+                     "traffic": NCU_TRAFFIC["gemm_c2"] * (tokens * cfg["dim"] + cfg["dim"] * cfg["ffn"] + tokens * cfg["ffn"])
+                     / (C2["tokens"] * C2["d_in"] + C2["d_in"] * C2["d_out"] + C2["tokens"] * C2["d_out"]),
+                     "traffic_source": NCU_TRAFFIC_SOURCE["gemm_c2"] + ", per launch, scaled to this layer by the sum of the three matrices' sizes",
                      "kernel": f"gemm_kernel<256, paired CTAs> fprop+dgrad+wgrad of a {cfg['dim']}x{cfg['ffn']} layer at {tokens} tokens",
                      "kernel_ms": gemm_ms, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)", "frac_of_nominal_9PF": gemm_tf / FP4_NOMINAL_TFLOPS},
         "kernels": {"c2_linear_gemm_tflops": c2_tf, "c2_ms": c2_ms, "c1_quantize_GBps": q_gbs, "c1_quantize_ms": q_ms,
@@ -493,7 +502,8 @@ def run_gemm(args, rank, world, device):
             "dtype": "e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out", "data": "synthetic",
             "config": {"workload": "C2: fprop, dgrad, wgrad GEMMs of a 4096x4096 layer at 8192 tokens per GPU on pre-quantised operands "
                                    "(token rows sharded across GPUs, no collective)", "l2": "3 rotated operand sets (~450 MB > L2)"},
-            "roofline": {"bound": "tensor", "achieved": tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf / fp4_peak, "traffic": None,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf / fp4_peak,
+                         "traffic": NCU_TRAFFIC["gemm_c2"], "traffic_source": NCU_TRAFFIC_SOURCE["gemm_c2"],
                          "kernel": "gemm_kernel<256, paired CTAs>", "kernel_ms": ms / 3, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)",
                          "frac_of_nominal_9PF": tf / FP4_NOMINAL_TFLOPS},
             "gpu_launches": 3 * args.steps, "clocks": clk.summary()}
@@ -546,7 +556,8 @@ def run_adamw(args, rank, world, device):
             "data": "synthetic",
             "config": {"workload": "compressed AdamW (balanced: half16_v8) on one 4096x8192 weight per GPU, BF16 gradient",
                        "l2": "3 rotated parameter sets (1 GB > L2)"},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                         "traffic": NCU_TRAFFIC["adamw"], "traffic_source": NCU_TRAFFIC_SOURCE["adamw"],
                          "kernel": "adamw_kernel<17,8,false,false,512>", "kernel_ms": ms, "peak_source": pk["source"]},
             "elements_per_s": ADAM_N / (ms * 1e-3), "gpu_launches": args.steps, "clocks": clk.summary()}
 
