@@ -15,11 +15,15 @@
 //             buffers need no barriers.  The scale blocks are read from shared memory once per k-tile: shared-memory
 //             bandwidth (operand reads by the tensor core + TMA writes) is what bounds this kernel, and moving the
 //             scales through registers with one warp per TMEM sub-partition read them four times.
-//   warps 2-9 epilogue, two per TMEM sub-partition, each owning half of the tile's columns.  For BF16 output a warp
-//             first drains its whole share: tcgen05.ld -> bf16(acc) -> x bf16(alpha), kept as packed BF16 pairs in
-//             registers; it then hands its half of the accumulator back to the MMA warp and only afterwards pushes the
-//             registers through a small swizzled staging buffer into TMA stores (which also crop).  The next tile's
-//             MMAs therefore wait for a drain of a few hundred cycles, not for the stores.
+//   warps 2-9 epilogue, two per TMEM sub-partition, eight 16-column units of the tile each.  For BF16 output a warp
+//             drains its units to registers: tcgen05.ld -> bf16(acc) -> x bf16(alpha), kept as packed BF16 pairs; with
+//             256-column tiles the two accumulator stages share 32 columns, each warp reads its shared unit first and
+//             arrives, which releases the next tile's MMAs, and only afterwards pushes the registers through a small
+//             swizzled staging buffer into TMA stores (which also crop).  The next tile's MMAs therefore wait for one
+//             16-column read, not for the drain or the stores.
+//   The producer and MMA warps run their loops converged and elect one lane per instruction (elect.sync): a loop that
+//   one lane entered alone makes every descriptor and coordinate a per-thread value that has to be moved into uniform
+//   registers before each TMA / tcgen05 instruction, which costs far more than the instructions themselves.
 // Every wait is bounded: on expiry the kernel raises the status word, all roles leave their loops, the producer
 // waits (bounded) for loads still in flight, TMEM is freed and the kernel returns.
 #include "common.cuh"
