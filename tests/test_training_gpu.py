@@ -88,7 +88,9 @@ def test_loss_decreases_and_matches_bf16_direction():
     nv.check_finite(model)
 
 
-def test_captured_steps_equal_eager_steps():
+@pytest.mark.parametrize("overlap", [True, False])
+def test_captured_steps_equal_eager_steps(overlap):
+    """overlap: optimizer updates recorded on a second stream beside the main line (the default) or in line."""
     import nvfp4_training as nv
     from nvfp4_training._runtime import load_runtime
     rng = load_runtime()[2]
@@ -99,6 +101,7 @@ def test_captured_steps_equal_eager_steps():
         nv.train_step(eager, mse, x, y)
     rng.reset_stats(100)
     graphed = nv.enable_nvfp4(make_model().cuda(), profile="balanced", lr=1e-3)
+    graphed.nvfp4_optimizer.overlap_updates = overlap
     with nv.capture_step(graphed, mse, x, y, steps=3) as graph:
         assert graph.sr_calls == 2 * 3 - 1 + 0 or graph.sr_calls > 0
         for _ in range(3):
