@@ -297,6 +297,25 @@ def split_init(src: np.ndarray, master: int):
     return hi, tail
 
 
+def e4m3_values() -> np.ndarray:
+    """float32 value of each of the 256 E4M3 codes (0x7f / 0xff are NaN)."""
+    L = lib()
+    return np.array([L.orc_e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+
+
+def fp8_decoded(p: np.ndarray, unit: np.ndarray) -> np.ndarray:
+    """master8.decoded (master8.py:14-23): BF16 bit patterns of e4m3(p) * unit[flat index // 512], same shape as p."""
+    flat = p.reshape(-1)
+    scale = np.repeat(np.asarray(unit, dtype=np.float32), 512)[: flat.size]
+    with np.errstate(invalid="ignore"):
+        return to_bf16_bits(e4m3_values()[flat] * scale).reshape(p.shape)
+
+
+def fp8_weight_pair(p: np.ndarray, unit: np.ndarray, pts_value: float):
+    """master8.encode (master8.py:36-56): both contraction directions of the decoded weight, RNE, one tensor scale."""
+    return weight_pair(fp8_decoded(p, unit), pts_value=pts_value)
+
+
 def philox(ctr, key):
     c = np.asarray(ctr, dtype=np.uint32); k = np.asarray(key, dtype=np.uint32); o = np.empty(4, dtype=np.uint32)
     lib().orc_philox4x32_10(_ptr(c), _ptr(k), _ptr(o))

@@ -104,3 +104,6 @@ if __name__ == "__main__":
     if which in ("all", "adamw"):
         from make_golden_adamw import make_adamw
         make_adamw(HERE / "adamw_reference.npz")
+    if which in ("all", "fp8"):
+        from make_golden_fp8 import make_fp8
+        make_fp8(HERE / "fp8_master_reference.npz")

@@ -127,3 +127,58 @@ def test_gemm_paired_and_single_forms_agree_with_the_oracle(native, pair, m, n, 
     step = np.abs(want) * 2.0 ** -7 + 1e-12
     assert (np.abs(got - want) <= 1.01 * step).all()
     assert (got == want).mean() > 0.98
+
+
+# ---- the benchmark configurations' own shapes -------------------------------------------------------------------------
+# (M, N, K) of out[M, N] = A[M, K] B[N, K]^T.  Linear-layer config: X[8192, 4096], W[4096, 4096]: fprop / dgrad and the
+# weight gradient, whose contraction runs over the 8192 tokens.  Decoder config (d 3072, FFN 8192, 8192 tokens): q/k/v/o
+# and down fprop, gate/up fprop, their dgrads and the three wgrad shapes.
+BASELINE_SHAPES = [(8192, 4096, 4096), (4096, 4096, 8192), (8192, 3072, 3072), (8192, 8192, 3072), (8192, 3072, 8192),
+                   (3072, 8192, 8192)]
+_BIG = {}
+
+
+def _big_case(native, m, n, k):
+    """Operands quantised on the GPU once per shape, with their oracle decodings (unscaled, and dequantised BF16)."""
+    key = (m, n, k)
+    if key not in _BIG:
+        _BIG.clear()   # one shape's worth of host memory at a time
+        a, b = _operands(native, m, n, k, seed=m + 3 * n + 7 * k)
+        host = [(t[0].cpu().numpy(), t[1].cpu().numpy(), float(t[2].item())) for t in (a, b)]
+        ua, ub = (O.decode_unscaled(h[0], h[1]) for h in host)
+        da = torch.from_numpy(O.dequantize(host[0][0], host[0][1], host[0][2], m, k)).bfloat16().cuda()
+        db = torch.from_numpy(O.dequantize(host[1][0], host[1][1], host[1][2], n, k)).bfloat16().cuda()
+        ref = (da @ db.t()).float()     # the BF16 matmul of the dequantised operands the accuracy criterion names
+        _BIG[key] = (a, b, host, ua, ub, ref)
+    return _BIG[key]
+
+
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("scaled", [True, False])
+@pytest.mark.parametrize("m,n,k", BASELINE_SHAPES)     # outermost: the four variants of a shape share its operands
+def test_gemm_at_benchmark_shapes(native, m, n, k, pair, scaled):
+    """Full-size GEMMs of the benchmark configurations (up to 32 k-tiles, several tiles per CTA with the accumulator stages
+    alternating): relative Frobenius error <= 1e-2 against a BF16 matmul of the oracle-dequantised operands over the
+    whole output, and the oracle's bits on a strided sample of rows and columns.  scaled=False is the raw BF16
+    accumulator image the optimizer decodes (no tensor scales)."""
+    a, b, host, ua, ub, ref = _big_case(native, m, n, k)
+    pts_a, pts_b = (a[2], b[2]) if scaled else (None, None)
+    out = native.gemm(a[0], a[1], pts_a, b[0], b[1], pts_b, rows=m, cols=n, out_dtype=torch.bfloat16, raw_bf16=True, pair=pair)
+    native.check_status()
+    got = out.float()
+    if scaled:
+        rel = ((got - ref).norm() / ref.norm()).item()
+        assert rel < 1e-2, rel
+    else:
+        alpha = host[0][2] * host[1][2]
+        rel = ((got * alpha - ref).norm() / ref.norm()).item()
+        assert rel < 1e-2, rel
+    ri = np.unique(np.concatenate([np.arange(0, m, 149), [127, 128, 255, 256, m - 129, m - 1]]))
+    ci = np.unique(np.concatenate([np.arange(0, n, 131), [127, 128, 255, 256, n - 129, n - 1]]))
+    raw = (torch.from_numpy(ua[ri]).double() @ torch.from_numpy(ub[ci]).double().t()).float().numpy()
+    sa, sb = (host[0][2], host[1][2]) if scaled else (1.0, 1.0)
+    want = O.rescale(raw, sa, sb, len(ri), len(ci), raw_bf16=True, out_bf16=True)
+    sample = got[torch.from_numpy(ri).cuda()][:, torch.from_numpy(ci).cuda()].cpu().numpy()
+    step = np.abs(want) * 2.0 ** -7 + 1e-12
+    assert (np.abs(sample - want) <= 1.01 * step).all()
+    assert (sample == want).mean() > 0.98

@@ -72,3 +72,40 @@ def test_plain_small_tensor_path_matches_reference(gold):
         for name, got in (("p", p), ("m", m), ("v", v)):
             assert np.array_equal(got.view(np.uint32), gold[f"plain_s{t}_{name}"].view(np.uint32)), (t, name)
         assert np.float32(amax) == gold[f"plain_s{t}_part"].max()
+
+
+@pytest.fixture(scope="module")
+def gold_fp8():
+    return np.load(GOLDEN / "fp8_master_reference.npz")
+
+
+def test_fp8_master_unit_growth_matches_reference(gold_fp8):
+    """tests/test_fp8_master_range.py:36-46 on the reference's own update kernel: an update beyond 448 x unit grows the
+    units of exactly the first and the last 512-block; every byte of the other blocks stays."""
+    g = gold_fp8
+    lr, b1, b2, eps, wd = (float(x) for x in g["hyper"])
+    p, unit = g["p0"].reshape(-1).copy(), g["unit0"].copy()
+    n = p.size
+    m, ms, vs = np.zeros(n, dtype=np.uint8), np.zeros(-(-n // 64), dtype=np.float32), np.zeros(-(-n // 64), dtype=np.float32)
+    for t in (1, 2):
+        part = O.adam_update("float8_m4v4_sqrt", p, g["grads"][t - 1], m, None, ms, vs, step=t, key=int(g["key"][0]),
+                             hyper=O.adam_hyper(lr, (b1, b2), eps, wd, t), unit=unit, grad_kind=0)
+        for name, got in (("p", p), ("unit", unit), ("m", m), ("ms", ms), ("vs", vs), ("part", part)):
+            want = g[f"s{t}_{name}"].reshape(-1)
+            assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), f"step {t} {name}"
+        if t == 1:
+            assert np.nonzero(unit > g["unit0"])[0].tolist() == [0, len(unit) - 1]
+            assert np.array_equal(p[512:-512], g["p0"].reshape(-1)[512:-512])
+            vals = O.from_bf16_bits(O.fp8_decoded(p, unit))
+            assert 0.22 < -vals[1] < 0.29 and 0.22 < vals[-1] < 0.29
+
+
+def test_fp8_master_encode_matches_reference(gold_fp8):
+    """master8.encode == pair(decoded weight): both NVFP4 orientations straight from E4M3 codes and per-block units."""
+    g = gold_fp8
+    for p, unit, dec, scale, outs in ((g["s2_p"], g["s2_unit"], g["decoded"], g["enc_scale"], ("enc_d", "enc_s", "enc_dt", "enc_st")),
+                                      (g["b_p"], g["b_unit"], g["b_decoded"], g["b_scale"], ("b_d", "b_s", "b_dt", "b_st"))):
+        assert np.array_equal(O.fp8_decoded(p, unit), dec)
+        row, col = O.fp8_weight_pair(p, unit, float(scale[0]))
+        assert np.array_equal(row[0], g[outs[0]]) and np.array_equal(row[1], g[outs[1]])
+        assert np.array_equal(col[0], g[outs[2]]) and np.array_equal(col[1], g[outs[3]])

@@ -52,6 +52,32 @@ def test_rescale_matches_reference(golden_quant, tag):
     assert np.array_equal(out.view(np.uint32), g[f"rescale_{tag}_out"].view(np.uint32))
 
 
+def _cuda_quant_names():
+    from conftest import GOLDEN
+    return [str(n) for n in np.load(GOLDEN / "cuda_quant_reference.npz")["names"]]
+
+
+@pytest.mark.parametrize("name", _cuda_quant_names())
+def test_quantize_matches_reference_cuda_kernels(golden_cuda_quant, name):
+    """quantize_cuda (csrc/kernels.cu:237-298) with quant_rows / quant_transpose / emit_group run on the host: row and
+    transposed orientation, strided views, SR x RHT, tensor scale (factor * max(amax, 1e-12)) * (1 / 2688)."""
+    from conftest import cuda_quant_case
+    x, sr, rht, seed, given, want = cuda_quant_case(golden_cuda_quant, name)
+    xn = x.view(torch.int16).numpy().view(np.uint16) if x.dtype == torch.bfloat16 else x.numpy()
+    got = O.quantize(xn, sr_mode=O.SR_HASH if sr else O.RNE, rht=rht, signs=golden_cuda_quant["signs"], seed=seed, pts_value=given)
+    assert np.float32(got[2]) == np.float32(want[2])
+    assert np.array_equal(got[1], want[1]), "scales"
+    assert np.array_equal(got[0], want[0]), "payload"
+
+
+def test_weight_pair_matches_reference_cuda_kernel(golden_cuda_quant):
+    """quant_weight_pair (csrc/kernels.cu:165-185)."""
+    g = golden_cuda_quant
+    row, col = O.weight_pair(g["pair_w"], pts_value=float(g["pair_pts"][0]))
+    assert np.array_equal(row[0], g["pair_data"]) and np.array_equal(row[1], g["pair_scale"])
+    assert np.array_equal(col[0], g["pair_data_t"]) and np.array_equal(col[1], g["pair_scale_t"])
+
+
 def test_philox_known_answers():
     # Random123 known-answer vectors for philox4x32-10
     kat = [([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),

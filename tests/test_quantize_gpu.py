@@ -157,3 +157,44 @@ def test_full_size_config_matches_oracle_and_round_trips(native):
                 back = native.dequantize(p, s, t, 4096, 4096).cpu()
                 rel = (back - x.float()).norm() / x.float().norm()
                 assert rel < 0.15
+
+
+def _cuda_quant_names():
+    from conftest import GOLDEN
+    return [str(n) for n in np.load(GOLDEN / "cuda_quant_reference.npz")["names"]]
+
+
+@pytest.mark.parametrize("name", _cuda_quant_names())
+def test_quantize_matches_reference_cuda_kernels(native, golden_cuda_quant, name):
+    """The `quantize` operator against outputs of the reference's own CUDA kernels (run on the host by
+    tests/golden/make_golden_cuda_quant.py): rows, transposed and strided views, SR x RHT, BF16 and FP32 sources."""
+    from conftest import cuda_quant_case
+    g = golden_cuda_quant
+    x, sr, rht, seed, given, want = cuda_quant_case(g, name)
+    kind = int(g[f"{name}_meta"][0])
+    base = (x.t() if kind == 1 else x).cuda() if kind != 2 else None
+    if kind == 2:
+        raw = g["base_" + str(g[f"{name}_base"])]
+        is_bf16 = int(g[f"{name}_meta"][1])
+        full = torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16) if is_bf16 else torch.from_numpy(raw)
+        xd = full.cuda()[::2, ::2]
+    else:
+        xd = base.t() if kind == 1 else base
+    assert xd.stride() == x.stride()
+    signs = torch.from_numpy(g["signs"]).cuda()
+    scale = None if given is None else torch.tensor(given, dtype=torch.float32, device="cuda")
+    mp, kp = native.round128(x.shape[0]), native.round128(x.shape[1])
+    packed, scales, pts = native.quantize(xd, signs, mp, kp, 2 if sr else 0, rht, seed, given_scale=scale)
+    assert np.float32(pts.item()) == np.float32(want[2])
+    _cmp(packed, scales, want)
+
+
+def test_weight_pair_matches_reference_cuda_kernel(native, golden_cuda_quant):
+    g = golden_cuda_quant
+    w = torch.from_numpy(g["pair_w"]).cuda()
+    pts = torch.from_numpy(g["pair_pts"]).cuda()
+    mp, kp = native.round128(w.shape[0]), native.round128(w.shape[1])
+    d, s, p, dt, st = native.quantize(w, signs_dev(), mp, kp, 0, False, 0, given_scale=pts.reshape(()), pair=True)
+    _cmp(d, s, (g["pair_data"], g["pair_scale"]))
+    _cmp(dt, st, (g["pair_data_t"], g["pair_scale_t"]))
+    assert np.float32(native.amax(w)[1].item()) == g["pair_pts"][0]
