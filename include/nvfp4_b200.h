@@ -1,14 +1,20 @@
 /*
  * C ABI of libnvfp4_b200.so — hand-written sm_100a CUDA kernels for the NVFP4 training hot path.
  *
- * Every entry point takes plain device pointers, sizes and a CUDA stream; none allocates, none
- * synchronises, none keeps global device state, so all of them are safe under CUDA-graph capture
- * (the quantiser's amax stage uses caller-provided scratch that must start zeroed once and then
- * resets itself).  Return value: NVFP4_OK or one of the codes below; nvfp4_last_error() gives the
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; none allocates and none
+ * synchronises.  With one exception none keeps device state of its own, so they are safe under
+ * CUDA-graph capture (the quantiser's amax stage uses caller-provided scratch that must start zeroed
+ * once and then resets itself).  The exception is nvfp4_quantize_static, whose scratch is an array
+ * inside the library image that all its calls on a device share; its comment states the rules that
+ * follow from that.  Return value: NVFP4_OK or one of the codes below; nvfp4_last_error() gives the
  * message of the calling thread's last failure.
  *
- * Each declaration names the reference interface it replaces (paths inside the reference
- * project xl03-bit/sm120-nvfp4-training).
+ * Each declaration names the reference interface it replaces (paths inside the reference project
+ * xl03-bit/sm120-nvfp4-training); nvfp4_quantize_static has no counterpart there and says so.
+ *
+ * `status` arguments: nullable device int that a kernel sets to NVFP4_ERR_TIMEOUT when one of its
+ * bounded device-side waits (on an asynchronous copy) gave up; the kernel then returns early
+ * instead of hanging.
  */
 #ifndef NVFP4_B200_H
 #define NVFP4_B200_H
@@ -41,7 +47,8 @@ enum { NVFP4_GEMM_RAW_BF16 = 1, NVFP4_GEMM_SINGLE_CTA = 2 };
 enum {
     NVFP4_Q_RHT = 1,        /* sign * H16 / 4 over each 16 contraction elements before scaling */
     NVFP4_Q_SR_HASH = 2,    /* stochastic rounding, the reference's 32-bit integer hash */
-    NVFP4_Q_SR_PHILOX = 4,  /* stochastic rounding, Philox4x32-10 keyed by the seed */
+    NVFP4_Q_SR_PHILOX = 4,  /* stochastic rounding by the hardware conversion (cvt.rs...e2m1x4) on Philox4x32-10 bits:
+                               one block per 16-element group, counter = group index, key = (seed, 0x4e564634) */
     NVFP4_Q_HI_FIRST = 8    /* even element in the high nibble (Comfy checkpoint order) */
 };
 
@@ -72,6 +79,8 @@ int nvfp4_amax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row
  * packed pointer to skip an orientation.  *_pts point at the FP32 tensor scale on the device,
  * *_flags are NVFP4_Q_* bits, *_seed the SR seed; seed_base (nullable, device int32[1]) is added to
  * both seeds on the device so that CUDA-graph replays draw fresh SR noise.  signs = 16 device floats.
+ * BF16 / FP16 sources with unit column stride and 16-byte aligned rows run on the persistent streaming kernel (TMA tile
+ * loads, TMA / bulk stores); every other source on a kernel with per-thread loads.  Same results.
  * Replaces quant_rows / quant_transpose / quant_weight_pair (csrc/kernels.cu:123-185; device-seed
  * variant csrc_graph/kernels.cu:126-127), _dual (act_pair.py:50-71), _pair (pair.py:25-36) and _single
  * (remat.py:7-19).
@@ -80,7 +89,17 @@ int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, in
                         const float* signs, const int32_t* seed_base,
                         uint8_t* row_packed, uint8_t* row_scales, const float* row_pts, int row_flags, uint32_t row_seed,
                         uint8_t* col_packed, uint8_t* col_scales, const float* col_pts, int col_flags, uint32_t col_seed,
-                        nvfp4_stream_t stream);
+                        int* status, nvfp4_stream_t stream);
+
+/*
+ * Both NVFP4 orientations (either may be null) of an FP8 master weight without a dense copy: w [rows][cols] contiguous
+ * E4M3 codes, element i worth e4m3(w[i]) * unit[i / 512] rounded to BF16; round to nearest, no Hadamard transform, one
+ * tensor scale `pts` for both packings.  Replaces master8._scaled_pair / encode and _decode
+ * (src/nvfp4_training/_backend/master8.py:14-23,36-56).
+ */
+int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, int64_t rows, int64_t cols, const float* pts,
+                              uint8_t* row_packed, uint8_t* row_scales, uint8_t* col_packed, uint8_t* col_scales,
+                              nvfp4_stream_t stream);
 
 /*
  * The reference's native operator `quantize` (src/nvfp4_training/_backend/csrc/bindings.cpp:9-12 over
@@ -92,7 +111,7 @@ int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, in
 int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,
                    int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,
                    const int32_t* seed_base, int pair, uint8_t* packed, uint8_t* scales, float* pts_out,
-                   uint8_t* packed_t, uint8_t* scales_t, void* scratch, nvfp4_stream_t stream);
+                   uint8_t* packed_t, uint8_t* scales_t, void* scratch, int* status, nvfp4_stream_t stream);
 
 /*
  * nvfp4_quantize for callers that cannot allocate device memory.  No counterpart in the reference project.
@@ -106,7 +125,8 @@ int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, i
  * NVFP4_ERR_ARG.  The call performs no cudaMalloc / cudaFree and uses no allocating library routine.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call outside any stream capture.  All calls on a device share the one array: calls that
- * may overlap on the GPU (different streams, no ordering) race on it and must be serialised by the caller.
+ * may overlap on the GPU (different streams, no ordering) race on it and must be serialised by the caller.  The address
+ * look-up itself is not synchronised: make the first call per device from one host thread.
  */
 int64_t nvfp4_quantize_static_max_elements(void);
 int nvfp4_quantize_static(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,

@@ -44,6 +44,7 @@ def lib():
         L.orc_e4m3_to_f32.restype = C.c_float; L.orc_e4m3_to_f32.argtypes = [C.c_uint8]
         L.orc_f32_to_e2m1_rne.restype = C.c_uint8; L.orc_f32_to_e2m1_rne.argtypes = [C.c_float]
         L.orc_e2m1_to_f32.restype = C.c_float; L.orc_e2m1_to_f32.argtypes = [C.c_uint8]
+        L.orc_cvt_rs_e2m1x4.restype = C.c_uint16; L.orc_cvt_rs_e2m1x4.argtypes = [C.c_float] * 4 + [C.c_uint32]
         L.orc_hash32.restype = C.c_uint32; L.orc_hash32.argtypes = [C.c_uint32, C.c_uint32]
         L.orc_philox4x32_10.restype = None
         L.orc_philox4x32_10.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]

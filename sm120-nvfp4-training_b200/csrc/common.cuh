@@ -130,9 +130,10 @@ __host__ __device__ __forceinline__ int64_t scale_offset(int64_t row, int64_t gr
 __device__ __forceinline__ float e4m3_normal_to_float(uint32_t x) {  // positive normal codes only
     return __uint_as_float(((x >> 3) + 120u) << 23 | (x & 7u) << 20);
 }
-__device__ __forceinline__ float e4m3_to_float(uint32_t x) {
+__device__ __forceinline__ float e4m3_to_float(uint32_t x) {   // codes 0x7f / 0xff are NaN
     uint32_t e = (x >> 3) & 15u, m = x & 7u;
     float v = e ? __uint_as_float((e + 120u) << 23 | m << 20) : static_cast<float>(m) * 0.001953125f;
+    if ((x & 127u) == 127u) v = __uint_as_float(0x7fc00000u);
     return (x & 128u) ? -v : v;
 }
 __device__ __forceinline__ float e2m1_to_float(uint32_t c) {

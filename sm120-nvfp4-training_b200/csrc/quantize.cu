@@ -1,13 +1,14 @@
-// NVFP4 quantiser for sm_100a: tensor amax, tile quantiser (row packing and/or transposed packing
-// from one read of the source), dequantiser.
+// NVFP4 quantiser for sm_100a: tensor amax, the two tile quantisers (row packing and/or transposed packing from one
+// read of the source), dequantiser.  The group arithmetic and its numerical contract live in quant_core.cuh.
 //
-// Numerical contract (bit exact against the CPU oracle): value = float(bf16_rne(x)); optional
-// sign * H16 / 4 butterfly over the 16 contraction elements; block scale
-// e4m3_rn(clamp((amax16 / 6) * (1 / pts), 2^-6, 448)); element q = clamp(v * ((1/pts) / scale), -6, 6)
-// rounded to e2m1 by the hardware cvt.rn.satfinite or stochastically between adjacent levels.
-// All float operations that take part in the contract are written with the _rn intrinsics so the
-// compiler can never contract them into FMAs.
-#include "common.cuh"
+//   quant_stream_kernel  persistent, warp-specialised: one warp streams 128 x 128 source tiles into a shared-memory ring
+//                        with TMA loads (out-of-range rows / columns arrive as zeros); eight warps encode from shared
+//                        memory, each into its own staging slabs, which leave by TMA stores.
+//                        Serves 2-byte sources with unit column stride and 16-byte aligned rows.
+//   quant_tile_kernel    one 128 x 128 tile per CTA with per-thread loads: every other source (FP32, E4M3 x unit,
+//                        arbitrary strides, unaligned bases).
+#include "quant_core.cuh"
+#include "async.cuh"
 
 #include <cstdarg>
 #include <cstring>
@@ -136,129 +137,36 @@ __global__ void __launch_bounds__(AMAX_THREADS) amax_kernel(const void* __restri
 }
 
 // ================================================================================================
-// group encoder
-// ================================================================================================
-// sign * H16 butterfly WITHOUT the final 1/4: that power-of-two factor is folded into the block
-// amax and the element multiplier by the caller, which gives the same bits as scaling the 16 values
-// first (a multiplication by 0.25 is exact).  The first stage absorbs the signs: a product with +-1
-// is exact, so fma(b, s_b, a * s_a) rounds once, exactly like (a * s_a) + (b * s_b).
-__device__ __forceinline__ void hadamard16_unscaled(float (&v)[16], const float (&sg)[16]) {
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-        const float a = __fmul_rn(v[2 * p], sg[2 * p]);
-        const float b = v[2 * p + 1], sb = sg[2 * p + 1];
-        v[2 * p] = __fmaf_rn(b, sb, a);
-        v[2 * p + 1] = __fmaf_rn(b, -sb, a);
-    }
-    // stages 2, 4, 8 pair whole (even, odd) couples: two-wide FP32 instructions, each half one IEEE rounding as before
-    // (x - y is fma(y, -1, x): the product is exact)
-    const float2 minus = make_float2(-1.f, -1.f);
-#pragma unroll
-    for (int d = 2; d < 16; d <<= 1) {
-#pragma unroll
-        for (int l = 0; l < 16; l += 2) {
-            if (l & d) continue;
-            const float2 lo = make_float2(v[l], v[l + 1]), hi = make_float2(v[l ^ d], v[(l ^ d) + 1]);
-            const float2 sum = __fadd2_rn(lo, hi), dif = __ffma2_rn(hi, minus, lo);
-            v[l] = sum.x; v[l + 1] = sum.y; v[l ^ d] = dif.x; v[(l ^ d) + 1] = dif.y;
-        }
-    }
-}
-
-constexpr int SR_NONE = 0, SR_HASH = 1, SR_PHILOX = 2;
-__host__ __device__ constexpr int sr_of_flags(int flags) {
-    return (flags & NVFP4_Q_SR_HASH) ? SR_HASH : (flags & NVFP4_Q_SR_PHILOX) ? SR_PHILOX : SR_NONE;
-}
-
-// Encodes 16 values (times `fold` = 0.25 when they come from hadamard16_unscaled, else 1).
-// idx0 = flat index of element 0 in the packing's padded coordinates (a multiple of 16).
-template <int SR>
-__device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float inv_pts, bool hi_first, uint32_t seed,
-                                          uint64_t idx0, uint32_t& scale_byte) {
-    float a = 0.f;
-#pragma unroll
-    for (int l = 0; l < 16; ++l) a = fmaxf(a, fabsf(v[l]));
-    if (fold) a = __fmul_rn(a, 0.25f);
-    const float enc = fminf(fmaxf(__fmul_rn(__fdiv_rn(a, 6.f), inv_pts), 0.015625f), 448.f);
-    const uint32_t e8 = __nv_cvt_float_to_fp8(enc, __NV_SATFINITE, __NV_E4M3);
-    scale_byte = e8;
-    float mul = __fdiv_rn(inv_pts, e4m3_normal_to_float(e8));
-    if (fold) mul = __fmul_rn(mul, 0.25f);
-    float q[16];   // v * mul, two per instruction
-    const float2 mul2 = make_float2(mul, mul);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-        const float2 t = __fmul2_rn(make_float2(v[2 * p], v[2 * p + 1]), mul2);
-        q[2 * p] = t.x; q[2 * p + 1] = t.y;
-    }
-    uint32_t lo = 0, hi = 0;
-    if constexpr (SR == SR_NONE) {
-        // cvt.rn.satfinite clamps to +-6 by itself
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const float q0 = q[2 * b], q1 = q[2 * b + 1], q2 = q[8 + 2 * b], q3 = q[8 + 2 * b + 1];
-            const float2 p0 = hi_first ? make_float2(q1, q0) : make_float2(q0, q1);
-            const float2 p1 = hi_first ? make_float2(q3, q2) : make_float2(q2, q3);
-            lo |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p0, __NV_E2M1, cudaRoundNearest)) << (8 * b);
-            hi |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(p1, __NV_E2M1, cudaRoundNearest)) << (8 * b);
-        }
-        return make_uint2(lo, hi);
-    } else {
-        uint32_t codes[16];
-        uint32_t rnd[8];
-        if constexpr (SR == SR_PHILOX) {
-            const uint64_t c0 = idx0 >> 3;  // one Philox block serves 8 consecutive elements (16 bits each)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const uint64_t ci = c0 + j;
-                const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(ci), static_cast<uint32_t>(ci >> 32), 0u, 0u),
-                                              seed, PHILOX_KEY1);
-                rnd[4 * j] = r.x; rnd[4 * j + 1] = r.y; rnd[4 * j + 2] = r.z; rnd[4 * j + 3] = r.w;
-            }
-        }
-        const uint32_t hbase = seed * 0x9e3779b9u + static_cast<uint32_t>(idx0) + 0x85ebca6bu;
-#pragma unroll
-        for (int l = 0; l < 16; ++l) {
-            const float ql = q[l];
-            // complement of the 24 random bits (the level choice adds it); Philox: 16-bit uniform on the 24-bit grid,
-            // whose complement is (~r16 << 8) | 0xff
-            uint32_t nh, bias = 0u;
-            if constexpr (SR == SR_HASH) nh = shr_mul(~hash32_mixed(hbase + l), 1u << 24);
-            else { nh = ((~rnd[l >> 1] >> ((l & 1) * 16)) & 0xffffu) << 8; bias = 0xffu; }
-            codes[l] = sr_code_signed(ql, nh, bias);   // sign bit set iff q < 0 (so -0 encodes as +0)
-        }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t e0 = codes[2 * b], o0 = codes[2 * b + 1], e1 = codes[8 + 2 * b], o1 = codes[8 + 2 * b + 1];
-            lo |= (hi_first ? ((e0 << 4) | o0) : (e0 | (o0 << 4))) << (8 * b);
-            hi |= (hi_first ? ((e1 << 4) | o1) : (e1 | (o1 << 4))) << (8 * b);
-        }
-        return make_uint2(lo, hi);
-    }
-}
-
-// ================================================================================================
 // tile quantiser: 128 x 128 source tile per CTA, 256 threads
 // ================================================================================================
-struct Orient {
-    uint8_t* packed;
-    uint8_t* scales;
-    const float* pts;
-    int64_t kp;  // padded contraction extent of this packing
-    uint32_t seed;
-    int flags;
-};
-
 constexpr int TILE = 128;
 constexpr int TILE_PITCH = TILE + 8;  // bf16 elements per smem row (272 B keeps 16-byte alignment)
 constexpr int COL_OUT_PITCH = 72;     // bytes per transposed payload row in smem (64 + 8: conflict-free 8-byte stores)
 
+// `unit` is read for E4M3 sources only: a contiguous weight whose element (r, c) is e4m3 * unit[(r * cols + c) / 512],
+// rounded to BF16 like every other source.
 template <int DT>
 __device__ __forceinline__ void load_group_bf16(const void* x, int64_t r, int64_t c0, int64_t rows, int64_t cols,
-                                                int64_t rs, int64_t cs, bool vec_ok, uint16_t (&h)[16]) {
+                                                int64_t rs, int64_t cs, bool vec_ok, const float* unit, uint16_t (&h)[16]) {
     if (r >= rows || c0 >= cols) {
 #pragma unroll
         for (int l = 0; l < 16; ++l) h[l] = 0;
+        return;
+    }
+    if constexpr (DT == NVFP4_E4M3) {
+        const uint8_t* src = static_cast<const uint8_t*>(x);
+        const int64_t flat = r * cols + c0;
+        if (vec_ok && c0 + 16 <= cols) {   // 16 codes in one 16-byte load; cols % 16 == 0, so they share a unit
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + flat));
+            const float scale = __ldg(unit + (flat >> 9));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int l = 0; l < 16; ++l) h[l] = bf16_bits(__fmul_rn(e4m3_to_float((w[l >> 2] >> (8 * (l & 3))) & 255u), scale));
+            return;
+        }
+#pragma unroll
+        for (int l = 0; l < 16; ++l)
+            h[l] = (c0 + l < cols) ? bf16_bits(__fmul_rn(e4m3_to_float(src[flat + l]), __ldg(unit + ((flat + l) >> 9)))) : uint16_t(0);
         return;
     }
     if (vec_ok && c0 + 16 <= cols) {
@@ -289,15 +197,18 @@ __device__ __forceinline__ void load_group_bf16(const void* x, int64_t r, int64_
         }
         return;
     }
+    if constexpr (DT != NVFP4_E4M3) {
 #pragma unroll
-    for (int l = 0; l < 16; ++l) h[l] = (c0 + l < cols) ? load_as_bf16<DT>(x, r * rs + (c0 + l) * cs) : uint16_t(0);
+        for (int l = 0; l < 16; ++l) h[l] = (c0 + l < cols) ? load_as_bf16<DT>(x, r * rs + (c0 + l) * cs) : uint16_t(0);
+    }
 }
 
 template <int DT, bool ROW, bool COL, int SR>
 __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restrict__ x, int64_t rows, int64_t cols,
                                                          int64_t rs, int64_t cs, int vec_ok,
                                                          const float* __restrict__ signs,
-                                                         const int32_t* __restrict__ seed_base, Orient R, Orient C) {
+                                                         const int32_t* __restrict__ seed_base,
+                                                         const float* __restrict__ unit, Orient R, Orient C) {
     __shared__ __align__(16) uint16_t tile[COL ? TILE * TILE_PITCH : 8];
     __shared__ __align__(16) uint8_t row_sc[ROW ? 1024 : 16];
     __shared__ __align__(16) uint8_t col_sc[COL ? 1024 : 16];
@@ -311,8 +222,8 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
     for (int l = 0; l < 16; ++l) sg[l] = __ldg(signs + l);
     const uint32_t base = seed_base ? static_cast<uint32_t>(__ldg(seed_base)) : 0u;
 
-    float inv_r = 0.f;
-    if constexpr (ROW) inv_r = __fdiv_rn(1.f, __ldg(R.pts));
+    ScaleMath sm_r{0.f, false};
+    if constexpr (ROW) sm_r = scale_math(__ldg(R.pts));
 
     // ---- phase A: each thread owns 4 row groups (16 consecutive columns of one row) ----------------
 #pragma unroll
@@ -321,7 +232,7 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
         const int lr = gi >> 3, gc = gi & 7;
         const int64_t r = r0 + lr, c = c0 + gc * 16;
         uint16_t h[16];
-        load_group_bf16<DT>(x, r, c, rows, cols, rs, cs, vec_ok != 0, h);
+        load_group_bf16<DT>(x, r, c, rows, cols, rs, cs, vec_ok != 0, unit, h);
         if constexpr (COL) {
             uint4 a, b;
             a.x = h[0] | (uint32_t(h[1]) << 16); a.y = h[2] | (uint32_t(h[3]) << 16);
@@ -338,8 +249,9 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
             const bool rht = R.flags & NVFP4_Q_RHT;
             if (rht) hadamard16_unscaled(v, sg);
             uint32_t sb;
-            uint2 p = encode16<SR>(v, rht, inv_r, R.flags & NVFP4_Q_HI_FIRST, R.seed + base,
-                                   static_cast<uint64_t>(r) * R.kp + c, sb);
+            const uint64_t idx0 = static_cast<uint64_t>(r) * R.kp + c;
+            uint2 p = encode16<SR, false>(v, rht, sm_r.inv, R.seed + base, static_cast<uint32_t>(idx0), idx0 >> 4, sb);
+            if (R.flags & NVFP4_Q_HI_FIRST) p = swap_nibbles(p);
             *reinterpret_cast<uint2*>(R.packed + r * (R.kp >> 1) + (c >> 1)) = p;
             row_sc[(gc >> 2) * 512 + (lr & 31) * 16 + (lr >> 5) * 4 + (gc & 3)] = static_cast<uint8_t>(sb);
         }
@@ -354,7 +266,7 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
     if constexpr (COL) {
         // ---- phase B: a thread takes two adjacent source columns (one 32-bit shared load per source row) and
         //      encodes source rows g*16 .. g*16+15 of each ----
-        const float inv_c = __fdiv_rn(1.f, __ldg(C.pts));
+        const ScaleMath sm_c = scale_math(__ldg(C.pts));
         const int cp = tid & 63;
         const bool c_rht = C.flags & NVFP4_Q_RHT, c_hi = C.flags & NVFP4_Q_HI_FIRST;
 #pragma unroll
@@ -371,7 +283,9 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
                 for (int l = 0; l < 16; ++l) v[l] = __uint_as_float(side ? (w[l] & 0xffff0000u) : (w[l] << 16));
                 if (c_rht) hadamard16_unscaled(v, sg);
                 uint32_t sb;
-                uint2 p = encode16<SR>(v, c_rht, inv_c, c_hi, C.seed + base, static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16), sb);
+                const uint64_t idx0 = static_cast<uint64_t>(c0 + n) * C.kp + (r0 + g * 16);
+                uint2 p = encode16<SR, false>(v, c_rht, sm_c.inv, C.seed + base, static_cast<uint32_t>(idx0), idx0 >> 4, sb);
+                if (c_hi) p = swap_nibbles(p);
                 *reinterpret_cast<uint2*>(col_out + n * COL_OUT_PITCH + g * 8) = p;
                 col_sc[(g >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (g & 3)] = static_cast<uint8_t>(sb);
             }
@@ -393,21 +307,319 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
 
 template <int DT, int SR>
 static void launch_tile_sr(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok, const float* signs,
-                           const int32_t* base, const Orient& R, const Orient& C, bool row, bool col, cudaStream_t st) {
+                           const int32_t* base, const float* unit, const Orient& R, const Orient& C, bool row, bool col,
+                           cudaStream_t st) {
     dim3 grid(static_cast<unsigned>(round128(rows) / 128), static_cast<unsigned>(round128(cols) / 128));
-    if (row && col) quant_tile_kernel<DT, true, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
-    else if (row) quant_tile_kernel<DT, true, false, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
-    else quant_tile_kernel<DT, false, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C);
+    if (row && col) quant_tile_kernel<DT, true, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
+    else if (row) quant_tile_kernel<DT, true, false, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
+    else quant_tile_kernel<DT, false, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
 }
 
 template <int DT>
-static int launch_tile(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok,
-                       const float* signs, const int32_t* base, const Orient& R, const Orient& C, bool row, bool col,
+static int launch_tile(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok, const float* signs,
+                       const int32_t* base, const float* unit, const Orient& R, const Orient& C, bool row, bool col,
                        cudaStream_t st) {
     const int sr = sr_of_flags(row ? R.flags : C.flags);
-    if (sr == SR_NONE) launch_tile_sr<DT, SR_NONE>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
-    else if (sr == SR_HASH) launch_tile_sr<DT, SR_HASH>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
-    else launch_tile_sr<DT, SR_PHILOX>(x, rows, cols, rs, cs, vec_ok, signs, base, R, C, row, col, st);
+    if (sr == SR_NONE) launch_tile_sr<DT, SR_NONE>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
+    else if constexpr (DT == NVFP4_E4M3) return NVFP4_ERR_UNSUPPORTED;   // master weights are rounded to nearest
+    else if (sr == SR_HASH) launch_tile_sr<DT, SR_HASH>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
+    else launch_tile_sr<DT, SR_PHILOX>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
+    return launch_status("nvfp4_quantize_tile");
+}
+
+// ================================================================================================
+// streaming quantiser: persistent CTAs, TMA tile loads into a shared-memory ring, TMA / bulk stores
+// ================================================================================================
+constexpr int QS_STAGES = 2;            // source tiles in flight per CTA (two CTAs per SM: four per SM, 128 KB)
+constexpr int QS_COMPUTE_WARPS = 8;
+constexpr int QS_THREADS = QS_COMPUTE_WARPS * 32 + 32;   // + the loading warp
+constexpr int QS_TILE_BYTES = TILE * TILE * 2;
+constexpr int QS_SLAB = TILE / QS_COMPUTE_WARPS;          // 16 packing rows per warp and orientation
+
+// What one encoding warp owns: two sets of payload slabs (16 rows of 64 bytes per orientation; a store may still be
+// reading one set while the next tile is written into the other) and the scale bytes of the current tile.
+struct __align__(128) WarpStage {
+    uint8_t row_out[2][QS_SLAB * 64];
+    uint8_t col_out[2][QS_SLAB * 64];
+    uint8_t row_sc[QS_SLAB * 8];
+    uint8_t col_sc[QS_SLAB * 8];
+};
+
+struct __align__(128) StreamSmem {
+    uint16_t in[QS_STAGES][TILE * TILE];   // dense rows of 256 bytes, as the tile load writes them
+    WarpStage stage[QS_COMPUTE_WARPS];
+    uint64_t full[QS_STAGES];
+    uint64_t empty[QS_STAGES];
+    int abort;
+};
+
+struct StreamArgs {
+    const float* signs;
+    const int32_t* seed_base;
+    int* status;          // nullable device int, raised when a bounded wait gave up
+    Orient R, C;
+    int tiles_r, tiles_c;
+};
+
+template <int DT>
+__device__ __forceinline__ void unpack16(const uint4 a, const uint4 b, float (&v)[16]) {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        if constexpr (DT == NVFP4_BF16) {
+            v[2 * t] = __uint_as_float(w[t] << 16);
+            v[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+        } else {   // FP16 -> FP32 is exact, then the one rounding to BF16 every source goes through
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+            v[2 * t] = bf16_value(bf16_bits(f.x));
+            v[2 * t + 1] = bf16_value(bf16_bits(f.y));
+        }
+    }
+}
+
+// The tile loop of one encoding warp.  FAST selects the division-free scale arithmetic; it is decided once per launch from
+// the tensor scales, so no group pays for a branch.
+template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT, bool FAST>
+__device__ __forceinline__ void stream_encode_loop(StreamSmem& S, const CUtensorMap* map_row, const CUtensorMap* map_col,
+                                                   const StreamArgs& a, const float (&sg)[16], float inv_r, float inv_c,
+                                                   int warp, int lane) {
+    using namespace aop;
+    const uint32_t base = a.seed_base ? static_cast<uint32_t>(__ldg(a.seed_base)) : 0u;
+    const uint32_t seed_r = a.R.seed + base, seed_c = a.C.seed + base;
+    WarpStage& W = S.stage[warp];
+    const int slab = warp * QS_SLAB;          // first packing row of this warp inside a tile
+    const int piece_row = slab + (lane >> 1), piece_half = lane & 1;   // the 4-byte scale piece this lane stores
+    const int piece_off = piece_half * 512 + (piece_row & 31) * 16 + (piece_row >> 5) * 4;
+    const int64_t gpr_r = a.R.kp >> 4, gpr_c = a.C.kp >> 4;            // groups per packing row
+    const int n_tiles = a.tiles_r * a.tiles_c;
+    int it = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+        const int s = it % QS_STAGES, buf = it & 1;
+        const int rt = t / a.tiles_c, ct = t - rt * a.tiles_c;
+        // the stores issued two tiles ago have finished reading the staging set that is written next
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / QS_STAGES) & 1, &S.abort))) break;
+        const uint16_t* tile = S.in[s];
+        if constexpr (ROW) {
+            // 16 source rows x 8 groups: a lane owns 4 groups; the warp reads 1 KB of consecutive bytes at a time
+            const uint64_t group0 = static_cast<uint64_t>(rt * TILE + slab) * gpr_r + ct * 8;
+            // all four groups' loads are issued before the first one is used
+            uint4 raw[4][2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4* src = reinterpret_cast<const uint4*>(tile + (slab + 4 * i + (lane >> 3)) * TILE + (lane & 7) * 16);
+                raw[i][0] = src[0]; raw[i][1] = src[1];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int lr = 4 * i + (lane >> 3), gc = lane & 7;
+                float v[16];
+                unpack16<DT>(raw[i][0], raw[i][1], v);
+                if constexpr (R_RHT) hadamard16_unscaled(v, sg);
+                const uint64_t group = group0 + static_cast<uint32_t>(lr * static_cast<int>(gpr_r) + gc);
+                uint32_t sb;
+                const uint2 p = encode16<SR, FAST>(v, R_RHT, inv_r, seed_r, static_cast<uint32_t>(group) << 4, group, sb);
+                *reinterpret_cast<uint2*>(&W.row_out[buf][lr * 64 + gc * 8]) = p;
+                W.row_sc[lr * 8 + gc] = static_cast<uint8_t>(sb);
+            }
+        }
+        if constexpr (COL) {
+            // 16 source columns x 8 groups of 16 source rows: a lane takes a pair of adjacent columns (one 32-bit shared
+            // load per source row) for two groups
+            const int cpl = lane & 7;
+            const uint64_t group0 = static_cast<uint64_t>(ct * TILE + slab) * gpr_c + rt * 8;
+            uint32_t wall[2][16];   // both groups' loads are issued before the first one is used
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int l = 0; l < 16; ++l)
+                    wall[i][l] = *reinterpret_cast<const uint32_t*>(tile + (((lane >> 3) + 4 * i) * 16 + l) * TILE + slab + 2 * cpl);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int g = (lane >> 3) + 4 * i;
+                const uint32_t (&w)[16] = wall[i];
+#pragma unroll
+                for (int side = 0; side < 2; ++side) {
+                    const int n = 2 * cpl + side;
+                    float v[16];
+#pragma unroll
+                    for (int l = 0; l < 16; ++l) {
+                        if constexpr (DT == NVFP4_BF16) v[l] = __uint_as_float(side ? (w[l] & 0xffff0000u) : (w[l] << 16));
+                        else {
+                            const __half hv = __ushort_as_half(static_cast<unsigned short>(side ? (w[l] >> 16) : (w[l] & 0xffffu)));
+                            v[l] = bf16_value(bf16_bits(__half2float(hv)));
+                        }
+                    }
+                    if constexpr (C_RHT) hadamard16_unscaled(v, sg);
+                    const uint64_t group = group0 + static_cast<uint32_t>(n * static_cast<int>(gpr_c) + g);
+                    uint32_t sb;
+                    const uint2 p = encode16<SR, FAST>(v, C_RHT, inv_c, seed_c, static_cast<uint32_t>(group) << 4, group, sb);
+                    *reinterpret_cast<uint2*>(&W.col_out[buf][n * 64 + g * 8]) = p;
+                    W.col_sc[n * 8 + g] = static_cast<uint8_t>(sb);
+                }
+            }
+        }
+        // this warp has read everything it needs from the source tile; its staging writes become visible to the copy
+        // engine and to the lanes that store the scale pieces
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.empty[s]);
+        if constexpr (ROW) {
+            const uint32_t piece = *reinterpret_cast<const uint32_t*>(&W.row_sc[(lane >> 1) * 8 + piece_half * 4]);
+            *reinterpret_cast<uint32_t*>(a.R.scales + (static_cast<int64_t>(rt) * (a.R.kp >> 6) + ct * 2) * 512 + piece_off) = piece;
+        }
+        if constexpr (COL) {
+            const uint32_t piece = *reinterpret_cast<const uint32_t*>(&W.col_sc[(lane >> 1) * 8 + piece_half * 4]);
+            *reinterpret_cast<uint32_t*>(a.C.scales + (static_cast<int64_t>(ct) * (a.C.kp >> 6) + rt * 2) * 512 + piece_off) = piece;
+        }
+        if (lane == 0) {
+            if constexpr (ROW) tma_store_2d(map_row, ct * 64, rt * TILE + slab, W.row_out[buf]);
+            if constexpr (COL) tma_store_2d(map_col, rt * 64, ct * TILE + slab, W.col_out[buf]);
+            bulk_commit();
+        }
+        __syncwarp();   // the scale bytes have been read before the next tile overwrites them
+    }
+    if (lane == 0) bulk_wait_all();
+}
+
+// Every encoding warp works on its own: of each 128 x 128 source tile it takes packing rows 16w .. 16w+15 of the row
+// orientation (source rows) and of the transposed orientation (source columns), stages the 1 KB payload slabs in its own
+// shared memory, hands them to the copy engine (one TMA store per slab) and writes its scale bytes as 4-byte pieces of the
+// swizzled blocks.  The only block-wide events are the ring's full / empty barriers.
+template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT>
+__global__ void __launch_bounds__(QS_THREADS, 2)
+quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_row,
+                    const __grid_constant__ CUtensorMap map_col, const StreamArgs a) {
+    using namespace aop;
+    extern __shared__ __align__(128) uint8_t stream_smem_raw[];
+    StreamSmem& S = *reinterpret_cast<StreamSmem*>(stream_smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = a.tiles_r * a.tiles_c;
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < QS_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], QS_COMPUTE_WARPS); }
+        S.abort = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == QS_COMPUTE_WARPS) {
+        // ---- loading warp: keeps the ring full --------------------------------------------------------------------
+        int it = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+            const int s = it % QS_STAGES;
+            if (it >= QS_STAGES) {
+                const bool ok = mbar_wait(&S.empty[s], ((it / QS_STAGES) - 1) & 1, &S.abort);
+                if (!__all_sync(0xffffffffu, ok)) break;
+            }
+            if (elect_one()) {
+                const int rt = t / a.tiles_c, ct = t - rt * a.tiles_c;
+                mbar_expect_tx(&S.full[s], QS_TILE_BYTES);
+                tma_load_2d(S.in[s], &map_in, ct * TILE, rt * TILE, &S.full[s]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- encoding warps -------------------------------------------------------------------------------------
+        float sg[16];
+#pragma unroll
+        for (int l = 0; l < 16; ++l) sg[l] = __ldg(a.signs + l);
+        ScaleMath sm_r{1.f, true}, sm_c{1.f, true};
+        if constexpr (ROW) sm_r = scale_math(__ldg(a.R.pts));
+        if constexpr (COL) sm_c = scale_math(__ldg(a.C.pts));
+        if (sm_r.fast && sm_c.fast)
+            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, true>(S, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
+        else
+            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, false>(S, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
+    }
+    __syncthreads();
+    if (tid == 0 && S.abort && a.status) *a.status = NVFP4_ERR_TIMEOUT;
+}
+
+static bool stream_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("NVFP4_QUANT_STREAM");
+        on = !(e && e[0] == '0');
+    }
+    return on != 0;
+}
+
+template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT>
+static cudaError_t launch_stream_one(const CUtensorMap& mi, const CUtensorMap& mr, const CUtensorMap& mc, const StreamArgs& a,
+                                     int grid, cudaStream_t st) {
+    const size_t smem = sizeof(StreamSmem);
+    static bool configured = false;   // one flag per kernel instantiation; the attribute belongs to the function
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(quant_stream_kernel<DT, ROW, COL, SR, R_RHT, C_RHT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    quant_stream_kernel<DT, ROW, COL, SR, R_RHT, C_RHT><<<grid, QS_THREADS, smem, st>>>(mi, mr, mc, a);
+    return cudaSuccess;
+}
+
+// Orientation / transform combinations the streaming kernel is built for: one orientation with or without the Hadamard
+// transform, both orientations without it (weights) or with it on the transposed one (activations, gradients).
+template <int DT, int SR>
+static cudaError_t launch_stream_sr(const CUtensorMap& mi, const CUtensorMap& mr, const CUtensorMap& mc, const StreamArgs& a,
+                                    bool row, bool col, int grid, cudaStream_t st) {
+    const bool rr = a.R.flags & NVFP4_Q_RHT, cr = a.C.flags & NVFP4_Q_RHT;
+    if (row && col) {
+        if (cr) return launch_stream_one<DT, true, true, SR, false, true>(mi, mr, mc, a, grid, st);
+        return launch_stream_one<DT, true, true, SR, false, false>(mi, mr, mc, a, grid, st);
+    }
+    if (row) {
+        if (rr) return launch_stream_one<DT, true, false, SR, true, false>(mi, mr, mc, a, grid, st);
+        return launch_stream_one<DT, true, false, SR, false, false>(mi, mr, mc, a, grid, st);
+    }
+    if (cr) return launch_stream_one<DT, false, true, SR, false, true>(mi, mr, mc, a, grid, st);
+    return launch_stream_one<DT, false, true, SR, false, false>(mi, mr, mc, a, grid, st);
+}
+
+// Returns NVFP4_ERR_UNSUPPORTED when the source does not qualify (the caller then uses the tile kernel).
+static int try_stream(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs, const float* signs,
+                      const int32_t* base, int* status, const Orient& R, const Orient& C, bool row, bool col, cudaStream_t st) {
+    if (!stream_enabled() || (dtype != NVFP4_BF16 && dtype != NVFP4_F16) || cs != 1) return NVFP4_ERR_UNSUPPORTED;
+    const int sr_mode = sr_of_flags(row ? R.flags : C.flags);
+    if (dtype == NVFP4_F16 && sr_mode != SR_NONE) return NVFP4_ERR_UNSUPPORTED;          // FP16 sources are master weights
+    if (((row ? R.flags : 0) | (col ? C.flags : 0)) & NVFP4_Q_HI_FIRST) return NVFP4_ERR_UNSUPPORTED;
+    if (row && col && (R.flags & NVFP4_Q_RHT)) return NVFP4_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (rs * 2) % 16 != 0 || rs < cols) return NVFP4_ERR_UNSUPPORTED;
+    const int64_t rp = round128(rows), cp = round128(cols);
+    if (rp / 128 * (cp / 128) > 0x7fffffffLL || rp > 0x7fffffffLL || cp > 0x7fffffffLL) return NVFP4_ERR_UNSUPPORTED;
+    CUtensorMap mi, mr, mc;
+    if (!aop::make_map_2d(&mi, dtype == NVFP4_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x,
+                          static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(rs) * 2, TILE, TILE))
+        return NVFP4_ERR_UNSUPPORTED;
+    mr = mi; mc = mi;
+    if (row && !aop::make_map_2d(&mr, CU_TENSOR_MAP_DATA_TYPE_UINT8, R.packed, static_cast<uint64_t>(cp / 2), static_cast<uint64_t>(rp),
+                                 static_cast<uint64_t>(cp / 2), 64, QS_SLAB))
+        return NVFP4_ERR_UNSUPPORTED;
+    if (col && !aop::make_map_2d(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT8, C.packed, static_cast<uint64_t>(rp / 2), static_cast<uint64_t>(cp),
+                                 static_cast<uint64_t>(rp / 2), 64, QS_SLAB))
+        return NVFP4_ERR_UNSUPPORTED;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    StreamArgs a{signs, base, status, R, C, static_cast<int>(rp / 128), static_cast<int>(cp / 128)};
+    const int64_t tiles = static_cast<int64_t>(a.tiles_r) * a.tiles_c;
+    const int grid = static_cast<int>(std::min<int64_t>(tiles, 2LL * sms));
+    cudaError_t e;
+    if (dtype == NVFP4_F16) e = launch_stream_sr<NVFP4_F16, SR_NONE>(mi, mr, mc, a, row, col, grid, st);
+    else if (sr_mode == SR_NONE) e = launch_stream_sr<NVFP4_BF16, SR_NONE>(mi, mr, mc, a, row, col, grid, st);
+    else if (sr_mode == SR_HASH) e = launch_stream_sr<NVFP4_BF16, SR_HASH>(mi, mr, mc, a, row, col, grid, st);
+    else e = launch_stream_sr<NVFP4_BF16, SR_PHILOX>(mi, mr, mc, a, row, col, grid, st);
+    if (e != cudaSuccess) {
+        set_error("nvfp4_quantize_tile: cannot configure the streaming kernel: %s", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
     return launch_status("nvfp4_quantize_tile");
 }
 
@@ -501,15 +713,14 @@ extern "C" int nvfp4_amax(const void* x, int dtype, int64_t rows, int64_t cols, 
     return launch_amax(x, dtype, rows, cols, rs, cs, scratch, out4, nullptr, 0, stream);
 }
 
-extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
-                                   const float* signs, const int32_t* seed_base, uint8_t* row_packed,
-                                   uint8_t* row_scales, const float* row_pts, int row_flags, uint32_t row_seed,
-                                   uint8_t* col_packed, uint8_t* col_scales, const float* col_pts, int col_flags,
-                                   uint32_t col_seed, nvfp4_stream_t stream) {
+static int quantize_tile_impl(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs, const float* signs,
+                              const int32_t* seed_base, const float* unit, uint8_t* row_packed, uint8_t* row_scales,
+                              const float* row_pts, int row_flags, uint32_t row_seed, uint8_t* col_packed, uint8_t* col_scales,
+                              const float* col_pts, int col_flags, uint32_t col_seed, int* status, nvfp4_stream_t stream) {
     NVFP4_REQUIRE(x && signs, NVFP4_ERR_ARG, "nvfp4_quantize_tile: null source or signs");
     NVFP4_REQUIRE(rows > 0 && cols > 0 && rs >= 0 && cs >= 0, NVFP4_ERR_ARG,
                   "nvfp4_quantize_tile: empty tensor or negative stride (rows=%lld cols=%lld)", (long long)rows, (long long)cols);
-    NVFP4_REQUIRE(dtype_ok(dtype), NVFP4_ERR_DTYPE, "nvfp4_quantize_tile: unsupported dtype code %d", dtype);
+    NVFP4_REQUIRE(dtype_ok(dtype) || (dtype == NVFP4_E4M3 && unit), NVFP4_ERR_DTYPE, "nvfp4_quantize_tile: unsupported dtype code %d", dtype);
     const bool row = row_packed != nullptr, col = col_packed != nullptr;
     NVFP4_REQUIRE(row || col, NVFP4_ERR_ARG, "nvfp4_quantize_tile: no output orientation requested");
     NVFP4_REQUIRE(!row || (row_scales && row_pts), NVFP4_ERR_ARG, "nvfp4_quantize_tile: row orientation needs scales and pts");
@@ -525,20 +736,45 @@ extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64
     for (const void* p : {static_cast<const void*>(row_packed), static_cast<const void*>(row_scales),
                           static_cast<const void*>(col_packed), static_cast<const void*>(col_scales)})
         NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_quantize_tile: outputs must be 16-byte aligned");
-    const int esz = dtype == NVFP4_F32 ? 4 : 2;
-    const int vec_ok = cs == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (rs * esz) % 16 == 0;
     Orient R{row_packed, row_scales, row_pts, cp, row_seed, row_flags};
     Orient C{col_packed, col_scales, col_pts, rp, col_seed, col_flags};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (dtype == NVFP4_F32) return launch_tile<NVFP4_F32>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, R, C, row, col, st);
-    if (dtype == NVFP4_BF16) return launch_tile<NVFP4_BF16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, R, C, row, col, st);
-    return launch_tile<NVFP4_F16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, R, C, row, col, st);
+    const int rc = try_stream(x, dtype, rows, cols, rs, cs, signs, seed_base, status, R, C, row, col, st);
+    if (rc != NVFP4_ERR_UNSUPPORTED) return rc;
+    const int esz = dtype == NVFP4_F32 ? 4 : dtype == NVFP4_E4M3 ? 1 : 2;
+    int vec_ok = cs == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (rs * esz) % 16 == 0;
+    if (dtype == NVFP4_E4M3) {
+        NVFP4_REQUIRE(cs == 1 && rs == cols, NVFP4_ERR_ARG, "nvfp4_quantize_fp8_weight: the weight must be contiguous");
+        return launch_tile<NVFP4_E4M3>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+    }
+    if (dtype == NVFP4_F32) return launch_tile<NVFP4_F32>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+    if (dtype == NVFP4_BF16) return launch_tile<NVFP4_BF16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+    return launch_tile<NVFP4_F16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+}
+
+extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+                                   const float* signs, const int32_t* seed_base, uint8_t* row_packed,
+                                   uint8_t* row_scales, const float* row_pts, int row_flags, uint32_t row_seed,
+                                   uint8_t* col_packed, uint8_t* col_scales, const float* col_pts, int col_flags,
+                                   uint32_t col_seed, int* status, nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(dtype != NVFP4_E4M3, NVFP4_ERR_DTYPE, "nvfp4_quantize_tile: E4M3 weights go through nvfp4_quantize_fp8_weight");
+    return quantize_tile_impl(x, dtype, rows, cols, rs, cs, signs, seed_base, nullptr, row_packed, row_scales, row_pts, row_flags,
+                              row_seed, col_packed, col_scales, col_pts, col_flags, col_seed, status, stream);
+}
+
+extern "C" int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, int64_t rows, int64_t cols, const float* pts,
+                                         uint8_t* row_packed, uint8_t* row_scales, uint8_t* col_packed, uint8_t* col_scales,
+                                         nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(w && unit && pts, NVFP4_ERR_ARG, "nvfp4_quantize_fp8_weight: null pointer");
+    static const float no_signs[16] = {};   // never read: this path has no Hadamard transform
+    return quantize_tile_impl(w, NVFP4_E4M3, rows, cols, cols, 1, no_signs, nullptr, unit, row_packed, row_scales, pts, 0, 0,
+                              col_packed, col_scales, pts, 0, 0, nullptr, stream);
 }
 
 extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp,
                               int64_t kp, int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,
                               const int32_t* seed_base, int pair, uint8_t* packed, uint8_t* scales, float* pts_out,
-                              uint8_t* packed_t, uint8_t* scales_t, void* scratch, nvfp4_stream_t stream) {
+                              uint8_t* packed_t, uint8_t* scales_t, void* scratch, int* status, nvfp4_stream_t stream) {
     NVFP4_REQUIRE(x && packed && scales && signs, NVFP4_ERR_ARG, "nvfp4_quantize: null pointer");
     NVFP4_REQUIRE(m > 0 && k > 0 && s0 >= 0 && s1 >= 0, NVFP4_ERR_ARG, "nvfp4_quantize: empty/broadcast/negative strides unsupported");
     NVFP4_REQUIRE(mp == round128(m) && kp == round128(k), NVFP4_ERR_ARG,
@@ -557,15 +793,16 @@ extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, in
     if (pair) {
         NVFP4_REQUIRE(!sr && !rht && s1 == 1 && s0 == k && packed_t && scales_t, NVFP4_ERR_ARG,
                       "nvfp4_quantize: paired encoding requires contiguous RNE weights and both outputs");
-        return nvfp4_quantize_tile(x, dtype, m, k, s0, s1, signs, seed_base, packed, scales, pts, 0, 0, packed_t, scales_t, pts, 0, 0, stream);
+        return nvfp4_quantize_tile(x, dtype, m, k, s0, s1, signs, seed_base, packed, scales, pts, 0, 0, packed_t, scales_t, pts, 0, 0,
+                                   status, stream);
     }
     if (s0 == 1 && s1 != 1) {
         // a transposed view of a row-major k x m matrix: its packing is the column orientation of that matrix
         return nvfp4_quantize_tile(x, dtype, k, m, s1, s0, signs, seed_base, nullptr, nullptr, nullptr, 0, 0, packed, scales, pts,
-                                   flags, seed, stream);
+                                   flags, seed, status, stream);
     }
     return nvfp4_quantize_tile(x, dtype, m, k, s0, s1, signs, seed_base, packed, scales, pts, flags, seed, nullptr, nullptr, nullptr,
-                               0, 0, stream);
+                               0, 0, status, stream);
 }
 
 extern "C" int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* pts, int64_t kp, int64_t rows,
@@ -623,5 +860,5 @@ extern "C" int nvfp4_quantize_static(const void* x, int dtype, int64_t m, int64_
                         reinterpret_cast<cudaStream_t>(stream));
     NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_quantize_static: cannot clear the ticket: %s", cudaGetErrorString(e));
     return nvfp4_quantize(x, dtype, m, k, s0, s1, mp, kp, sr, rht, seed, signs, nullptr, seed_base, 0, packed, scales, pts_out,
-                          nullptr, nullptr, scratch, stream);
+                          nullptr, nullptr, scratch, nullptr, stream);
 }

@@ -28,8 +28,9 @@ _SIGNATURES = {
     "nvfp4_version": (I32, []),
     "nvfp4_amax_scratch_bytes": (I64, []),
     "nvfp4_amax": (I32, [P, I32, I64, I64, I64, I64, P, P, P]),
-    "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P]),
-    "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P]),
+    "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P, P]),
+    "nvfp4_quantize_fp8_weight": (I32, [P, P, I64, I64, P, P, P, P, P, P]),
+    "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P, P]),
     "nvfp4_quantize_static_max_elements": (I64, []),
     "nvfp4_quantize_static": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, P, P, P]),
     "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
@@ -135,7 +136,7 @@ def quantize_tile(x, signs, *, row=None, col=None, seed_base=None):
     with torch.cuda.device(x.device):
         check(lib().nvfp4_quantize_tile(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1),
                                         signs.data_ptr(), ptr(seed_base), rp, rs, rq, rf, rsd, cp, cs, cq, cf, csd,
-                                        stream_of(x)))
+                                        status_word(x.device).data_ptr(), stream_of(x)))
 
 
 def quantize(x, signs, mp, kp, sr, rht, seed, given_scale=None, pair=False, seed_base=None):
@@ -155,8 +156,28 @@ def quantize(x, signs, mp, kp, sr, rht, seed, given_scale=None, pair=False, seed
                                    int(sr), int(bool(rht)), int(seed) & 0xFFFFFFFF, signs.data_ptr(), ptr(given_scale),
                                    ptr(seed_base), int(bool(pair)), packed.data_ptr(), scales.data_ptr(),
                                    None if given_scale is not None else pts.data_ptr(), ptr(dt), ptr(st),
-                                   scratch(dev).data_ptr(), stream_of(x)))
+                                   scratch(dev).data_ptr(), status_word(dev).data_ptr(), stream_of(x)))
     return [packed, scales, pts, dt, st] if pair else [packed, scales, pts]
+
+
+def quantize_fp8_weight(w, unit, pts, *, row=True, col=True):
+    """Both orientations (or one) of an E4M3 master weight with per-512 units: (d, s, dt, st), None where not asked."""
+    m, k = w.shape
+    mp, kp = round128(m), round128(k)
+    dev = w.device
+    d = s = dt = st = None
+    if row:
+        d = torch.empty((mp, kp // 2), dtype=torch.uint8, device=dev)
+        s = torch.empty((mp // 128 * 32, kp // 64 * 16), dtype=torch.uint8, device=dev)
+    if col:
+        dt = torch.empty((kp, mp // 2), dtype=torch.uint8, device=dev)
+        st = torch.empty((kp // 128 * 32, mp // 64 * 16), dtype=torch.uint8, device=dev)
+    if not w.is_contiguous():
+        raise ValueError("FP8 master weights must be contiguous")
+    with torch.cuda.device(dev):
+        check(lib().nvfp4_quantize_fp8_weight(w.data_ptr(), unit.data_ptr(), m, k, pts.data_ptr(), ptr(d), ptr(s), ptr(dt), ptr(st),
+                                              stream_of(w)))
+    return d, s, dt, st
 
 
 def dequantize(packed, scales, pts, rows, cols, *, hi_first=False, dtype=torch.float32):

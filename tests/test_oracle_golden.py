@@ -78,6 +78,17 @@ def test_weight_pair_matches_reference_cuda_kernel(golden_cuda_quant):
     assert np.array_equal(col[0], g["pair_data_t"]) and np.array_equal(col[1], g["pair_scale_t"])
 
 
+def test_hardware_stochastic_conversion_model():
+    """The oracle's model of cvt.rs.satfinite.e2m1x4.f32 against the instruction's outputs recorded on a B200
+    (tests/golden/cvt_rs_probe.cu): single operands against every byte of the random word, and random quadruples."""
+    from conftest import GOLDEN
+    g = np.load(GOLDEN / "cvt_rs_e2m1x4.npz")
+    L = O.lib()
+    got = np.array([L.orc_cvt_rs_e2m1x4(float(a), float(b), float(c), float(d), int(r))
+                    for a, b, c, d, r in zip(g["a"], g["b"], g["c"], g["d"], g["rbits"])], dtype=np.uint16)
+    assert np.array_equal(got, g["out"])
+
+
 def test_philox_known_answers():
     # Random123 known-answer vectors for philox4x32-10
     kat = [([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),
