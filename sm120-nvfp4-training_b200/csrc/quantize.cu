@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
     const int64_t r0 = rt * TILE, c0 = ct * TILE;
     float sg[16];
 #pragma unroll
-    for (int l = 0; l < 16; ++l) sg[l] = __ldg(signs + l);
+    for (int l = 0; l < 16; ++l) sg[l] = signs ? __ldg(signs + l) : 1.f;   // null: no orientation uses the transform
     const uint32_t base = seed_base ? static_cast<uint32_t>(__ldg(seed_base)) : 0u;
 
     ScaleMath sm_r{0.f, false};
@@ -524,7 +524,7 @@ quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_con
         // ---- encoding warps -------------------------------------------------------------------------------------
         float sg[16];
 #pragma unroll
-        for (int l = 0; l < 16; ++l) sg[l] = __ldg(a.signs + l);
+        for (int l = 0; l < 16; ++l) sg[l] = a.signs ? __ldg(a.signs + l) : 1.f;
         ScaleMath sm_r{1.f, true}, sm_c{1.f, true};
         if constexpr (ROW) sm_r = scale_math(__ldg(a.R.pts));
         if constexpr (COL) sm_c = scale_math(__ldg(a.C.pts));
@@ -717,7 +717,8 @@ static int quantize_tile_impl(const void* x, int dtype, int64_t rows, int64_t co
                               const int32_t* seed_base, const float* unit, uint8_t* row_packed, uint8_t* row_scales,
                               const float* row_pts, int row_flags, uint32_t row_seed, uint8_t* col_packed, uint8_t* col_scales,
                               const float* col_pts, int col_flags, uint32_t col_seed, int* status, nvfp4_stream_t stream) {
-    NVFP4_REQUIRE(x && signs, NVFP4_ERR_ARG, "nvfp4_quantize_tile: null source or signs");
+    NVFP4_REQUIRE(x, NVFP4_ERR_ARG, "nvfp4_quantize_tile: null source");
+    NVFP4_REQUIRE(signs || !((row_flags | col_flags) & NVFP4_Q_RHT), NVFP4_ERR_ARG, "nvfp4_quantize_tile: the Hadamard transform needs the sign vector");
     NVFP4_REQUIRE(rows > 0 && cols > 0 && rs >= 0 && cs >= 0, NVFP4_ERR_ARG,
                   "nvfp4_quantize_tile: empty tensor or negative stride (rows=%lld cols=%lld)", (long long)rows, (long long)cols);
     NVFP4_REQUIRE(dtype_ok(dtype) || (dtype == NVFP4_E4M3 && unit), NVFP4_ERR_DTYPE, "nvfp4_quantize_tile: unsupported dtype code %d", dtype);
@@ -766,8 +767,8 @@ extern "C" int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, in
                                          uint8_t* row_packed, uint8_t* row_scales, uint8_t* col_packed, uint8_t* col_scales,
                                          nvfp4_stream_t stream) {
     NVFP4_REQUIRE(w && unit && pts, NVFP4_ERR_ARG, "nvfp4_quantize_fp8_weight: null pointer");
-    static const float no_signs[16] = {};   // never read: this path has no Hadamard transform
-    return quantize_tile_impl(w, NVFP4_E4M3, rows, cols, cols, 1, no_signs, nullptr, unit, row_packed, row_scales, pts, 0, 0,
+    // no sign vector: this path has no Hadamard transform (every pointer a kernel receives must be a device address)
+    return quantize_tile_impl(w, NVFP4_E4M3, rows, cols, cols, 1, nullptr, nullptr, unit, row_packed, row_scales, pts, 0, 0,
                               col_packed, col_scales, pts, 0, 0, nullptr, stream);
 }
 

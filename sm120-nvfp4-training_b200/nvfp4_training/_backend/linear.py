@@ -45,6 +45,17 @@ def _source(w: torch.Tensor) -> torch.Tensor:
     return decoded(w) if w.dtype == torch.float8_e4m3fn else w.detach()
 
 
+def _is_fp8(w: torch.Tensor) -> bool:
+    return w.dtype == torch.float8_e4m3fn and w.is_contiguous() and getattr(w, "_v6_unit", None) is not None
+
+
+def encode(w: torch.Tensor, scale: torch.Tensor, *, row: bool = True, trans: bool = True):
+    """FP8 master -> (d, s, scale, dt, st) straight from the E4M3 codes and their per-512 units, no dense copy
+    (master8.encode, master8.py:50-56); orientations that are not asked for come back as None."""
+    d, s, dt, st = quant.nat.quantize_fp8_weight(w.detach().view(torch.uint8), w._v6_unit, scale, row=row, col=trans)
+    return d, s, scale, dt, st
+
+
 def grad_quant(g, signs, w, rht=False):
     """SR quantisation of a gradient; under graph replay the seed is offset + device base (nvfp4_v5.py:19-32)."""
     clock = getattr(w, "_v5_clock", None)
@@ -69,20 +80,27 @@ class _LinearFn(torch.autograd.Function):
             a, xp = dual(x2, signs)
         else:
             a = quantize(x2, signs=signs)
-        src = _source(w)
-        contiguous = src.is_contiguous()
+        fp8 = _is_fp8(w)
+        contiguous = w.is_contiguous()
         remat = getattr(w, "_v6_remat", False) and contiguous
         paired = not remat and need_x and contiguous
+        # FP8 masters are read by the quantiser as they are stored; only a missing tensor scale (the first step of a
+        # model, before the optimizer has published one) needs the dense BF16 image
+        src = w.detach() if (fp8 and pts is not None) else _source(w)
         if pts is None and (paired or remat):
             pts = weight_scale(src)
         if paired:
-            data, scale, pts, td, ts = pair(src, pts)
+            data, scale, pts, td, ts = encode(w, pts) if fp8 else pair(src, pts)
             b = Packed(data, scale, pts, w.dtype)
             _STATS["quant"] += 2
             _STATS["reused_weight_amax"] += 1
             _STATS["v5_pair"] += 1
         elif remat:
-            wd, ws = single(src, pts, False)
+            wd, ws = encode(w, pts, trans=False)[:2] if fp8 else single(src, pts, False)
+            b = Packed(wd, ws, pts, w.dtype)
+            _STATS["quant"] += 1
+        elif fp8 and pts is not None:
+            wd, ws = encode(w, pts, trans=False)[:2]
             b = Packed(wd, ws, pts, w.dtype)
             _STATS["quant"] += 1
         else:
@@ -123,11 +141,15 @@ class _LinearFn(torch.autograd.Function):
         if ctx.need_x:
             aq = ahead if ahead is not None else grad_quant(g, signs, w)
             if ctx.remat:
-                wd, ws = single(_source(w), wpts, True)
+                wd, ws = encode(w, wpts, row=False)[3:] if _is_fp8(w) else single(_source(w), wpts, True)
                 wq = Packed(wd, ws, wpts, w.dtype)
                 _STATS["quant"] += 1
             elif ctx.paired:
                 wq = Packed(saved[-2], saved[-1], wpts, w.dtype)
+            elif _is_fp8(w):
+                wd, ws = encode(w, wpts, row=False)[3:]
+                wq = Packed(wd, ws, wpts, w.dtype)
+                _STATS["quant"] += 1
             else:
                 wq = quantize(_source(w).t(), signs=signs, pts=wpts)
             dx = matmul(aq, wq, rows=ctx.m, cols=ctx.k, output_dtype=ctx.xdtype)
