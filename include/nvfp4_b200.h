@@ -92,6 +92,19 @@ int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, in
                         int* status, nvfp4_stream_t stream);
 
 /*
+ * nvfp4_quantize_tile for a source whose producer left its amax on the device (a kernel of this library that ends in an
+ * atomic maximum, see the workload helpers below): the tensor scales are computed inside the quantiser as
+ * (factor * max(amax[0], 1e-12)) * (1 / 2688), factor 4 for an orientation under the Hadamard transform, 1 otherwise, and
+ * written to row_pts / col_pts; no separate pass over the source.  Same results as nvfp4_amax + nvfp4_quantize_tile, which
+ * replace _absmax + _scale + _dual (src/nvfp4_training/_backend/act_pair.py:9-21,50-71).
+ */
+int nvfp4_quantize_tile_amax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
+                             const float* signs, const int32_t* seed_base, const float* amax,
+                             uint8_t* row_packed, uint8_t* row_scales, float* row_pts, int row_flags, uint32_t row_seed,
+                             uint8_t* col_packed, uint8_t* col_scales, float* col_pts, int col_flags, uint32_t col_seed,
+                             int* status, nvfp4_stream_t stream);
+
+/*
  * Both NVFP4 orientations (either may be null) of an FP8 master weight without a dense copy: w [rows][cols] contiguous
  * E4M3 codes, element i worth e4m3(w[i]) * unit[i / 512] rounded to BF16; round to nearest, no Hadamard transform, one
  * tensor scale `pts` for both packings.  Replaces master8._scaled_pair / encode and _decode
@@ -200,16 +213,33 @@ int nvfp4_adamw_plain(float* p, const float* grad, float* m, float* v, int64_t n
 int nvfp4_split_init(const float* src, int64_t n, int master, void* hi, int8_t* tail, nvfp4_stream_t stream);
 
 /*
- * Workload helpers (BF16, element-wise, fused): rotary position embedding on [tokens][heads][dim] rows (split-half
- * convention, tables cos/sin [seq][dim/2], inverse != 0 applies the transpose rotation = the backward pass), and SwiGLU
- * gating out = silu(gate) * up (dout == NULL) or its backward (dgate -> out_or_dgate, dup).  The reference keeps a rotary
+ * Workload helpers: the BF16 element-wise operations that sit between the NVFP4 layers of the benchmarked decoder, each
+ * fused with what surrounds it and with the tensor amax of its result.  `amax` arguments are nullable device floats that
+ * must hold 0 (or an earlier maximum) on entry and receive max |result| by an atomic maximum, so that the quantiser of
+ * the next NVFP4 layer needs no pass of its own over the tensor (nvfp4_quantize_tile_amax).  The reference keeps a rotary
  * kernel for one of its model integrations (src/precision_lora/_packed_cuda.py:104-114) and otherwise leaves these
- * operations to PyTorch; they are here because they sit between the NVFP4 layers of the benchmarked decoder.
+ * operations to PyTorch (src/nvfp4_training/_workloads/lm.py).
+ *
+ * nvfp4_rope: rotary position embedding on [tokens][heads][dim] rows with input / output row pitches in elements (split-
+ * half convention, tables cos / sin [seq][dim / 2]); mode 0 rotates, 1 applies the inverse rotation (the backward pass),
+ * 2 copies (the un-rotated part of a fused q / k / v gradient).
+ * nvfp4_swiglu: out = silu(gate) * up (dout == NULL), or its backward (dgate -> out_or_dgate, dup); every operand is
+ * [rows][cols] with its own row pitch, so the halves of a fused gate / up projection are used in place.
+ * nvfp4_add_rmsnorm: sum = x + delta (skipped when delta == NULL), h = sum * rsqrt(mean(sum^2) + eps) * bf16(gamma),
+ * rstd kept for the backward pass.
+ * nvfp4_rmsnorm_bwd: dx = d(h -> sum) + dres (dres nullable: the gradient arriving on the residual path) and dgamma;
+ * `partial` is FP32 scratch of nvfp4_rmsnorm_bwd_partials(rows, cols) x cols elements, reduced in a fixed order.
  */
 int nvfp4_rope(const void* x, void* out, const void* cos_t, const void* sin_t, int64_t tokens, int seq, int heads, int dim,
-               int64_t pitch, int inverse, nvfp4_stream_t stream);
-int nvfp4_swiglu(const void* gate, const void* up, const void* dout, void* out_or_dgate, void* dup, int64_t n,
+               int64_t pitch, int64_t out_pitch, int mode, float* amax, nvfp4_stream_t stream);
+int nvfp4_swiglu(const void* gate, int64_t gate_pitch, const void* up, int64_t up_pitch, const void* dout, int64_t dout_pitch,
+                 void* out_or_dgate, int64_t out_pitch, void* dup, int64_t dup_pitch, int64_t rows, int64_t cols, float* amax,
                  nvfp4_stream_t stream);
+int nvfp4_add_rmsnorm(const void* x, const void* delta, const float* gamma, float eps, int64_t rows, int64_t cols, void* sum_out,
+                      void* h_out, float* rstd_out, float* amax_out, nvfp4_stream_t stream);
+int64_t nvfp4_rmsnorm_bwd_partials(int64_t rows, int64_t cols);
+int nvfp4_rmsnorm_bwd(const void* dh, const void* sum, const float* rstd, const float* gamma, const void* dres, int64_t rows,
+                      int64_t cols, void* dx, float* partial, float* dgamma, float* amax_out, nvfp4_stream_t stream);
 
 /*
  * ---- frozen NVFP4 checkpoints in "Comfy" order as LoRA bases ------------------------------------------------------

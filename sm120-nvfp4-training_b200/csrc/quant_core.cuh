@@ -166,10 +166,21 @@ __device__ __forceinline__ uint2 encode16(const float (&v)[16], bool fold, float
     return make_uint2(lo, hi);
 }
 
+// Tensor scale of one orientation: read from `pts`, or, when a producer kernel left the tensor's amax on the device,
+// computed from it with the expression of the amax kernel, (factor * max(amax, 1e-12)) * (1 / 2688) with factor 4 under
+// the Hadamard transform, and written to `pts` by the first thread of the grid (the GEMM reads it from there).
+__device__ __forceinline__ float tensor_scale(const float* amax, float* pts, bool rht, bool writer) {
+    if (!amax) return __ldg(pts);
+    const float a = fmaxf(bf16_value(bf16_bits(__ldg(amax))), 1.e-12f);
+    const float v = __fmul_rn(__fmul_rn(rht ? 4.f : 1.f, a), 1.f / (6.f * 448.f));
+    if (writer) *pts = v;
+    return v;
+}
+
 struct Orient {
     uint8_t* packed;
     uint8_t* scales;
-    const float* pts;
+    float* pts;
     int64_t kp;  // padded contraction extent of this packing
     uint32_t seed;
     int flags;

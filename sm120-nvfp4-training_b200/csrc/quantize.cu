@@ -208,7 +208,8 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
                                                          int64_t rs, int64_t cs, int vec_ok,
                                                          const float* __restrict__ signs,
                                                          const int32_t* __restrict__ seed_base,
-                                                         const float* __restrict__ unit, Orient R, Orient C) {
+                                                         const float* __restrict__ unit, const float* __restrict__ amax,
+                                                         Orient R, Orient C) {
     __shared__ __align__(16) uint16_t tile[COL ? TILE * TILE_PITCH : 8];
     __shared__ __align__(16) uint8_t row_sc[ROW ? 1024 : 16];
     __shared__ __align__(16) uint8_t col_sc[COL ? 1024 : 16];
@@ -222,8 +223,9 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
     for (int l = 0; l < 16; ++l) sg[l] = signs ? __ldg(signs + l) : 1.f;   // null: no orientation uses the transform
     const uint32_t base = seed_base ? static_cast<uint32_t>(__ldg(seed_base)) : 0u;
 
+    const bool writer = tid == 0 && blockIdx.x == 0 && blockIdx.y == 0;
     ScaleMath sm_r{0.f, false};
-    if constexpr (ROW) sm_r = scale_math(__ldg(R.pts));
+    if constexpr (ROW) sm_r = scale_math(tensor_scale(amax, R.pts, R.flags & NVFP4_Q_RHT, writer));
 
     // ---- phase A: each thread owns 4 row groups (16 consecutive columns of one row) ----------------
 #pragma unroll
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
     if constexpr (COL) {
         // ---- phase B: a thread takes two adjacent source columns (one 32-bit shared load per source row) and
         //      encodes source rows g*16 .. g*16+15 of each ----
-        const ScaleMath sm_c = scale_math(__ldg(C.pts));
+        const ScaleMath sm_c = scale_math(tensor_scale(amax, C.pts, C.flags & NVFP4_Q_RHT, writer));
         const int cp = tid & 63;
         const bool c_rht = C.flags & NVFP4_Q_RHT, c_hi = C.flags & NVFP4_Q_HI_FIRST;
 #pragma unroll
@@ -307,23 +309,23 @@ __global__ void __launch_bounds__(256, 4) quant_tile_kernel(const void* __restri
 
 template <int DT, int SR>
 static void launch_tile_sr(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok, const float* signs,
-                           const int32_t* base, const float* unit, const Orient& R, const Orient& C, bool row, bool col,
-                           cudaStream_t st) {
+                           const int32_t* base, const float* unit, const float* amax, const Orient& R, const Orient& C, bool row,
+                           bool col, cudaStream_t st) {
     dim3 grid(static_cast<unsigned>(round128(rows) / 128), static_cast<unsigned>(round128(cols) / 128));
-    if (row && col) quant_tile_kernel<DT, true, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
-    else if (row) quant_tile_kernel<DT, true, false, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
-    else quant_tile_kernel<DT, false, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C);
+    if (row && col) quant_tile_kernel<DT, true, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C);
+    else if (row) quant_tile_kernel<DT, true, false, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C);
+    else quant_tile_kernel<DT, false, true, SR><<<grid, 256, 0, st>>>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C);
 }
 
 template <int DT>
 static int launch_tile(const void* x, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int vec_ok, const float* signs,
-                       const int32_t* base, const float* unit, const Orient& R, const Orient& C, bool row, bool col,
-                       cudaStream_t st) {
+                       const int32_t* base, const float* unit, const float* amax, const Orient& R, const Orient& C, bool row,
+                       bool col, cudaStream_t st) {
     const int sr = sr_of_flags(row ? R.flags : C.flags);
-    if (sr == SR_NONE) launch_tile_sr<DT, SR_NONE>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
+    if (sr == SR_NONE) launch_tile_sr<DT, SR_NONE>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C, row, col, st);
     else if constexpr (DT == NVFP4_E4M3) return NVFP4_ERR_UNSUPPORTED;   // master weights are rounded to nearest
-    else if (sr == SR_HASH) launch_tile_sr<DT, SR_HASH>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
-    else launch_tile_sr<DT, SR_PHILOX>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, R, C, row, col, st);
+    else if (sr == SR_HASH) launch_tile_sr<DT, SR_HASH>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C, row, col, st);
+    else launch_tile_sr<DT, SR_PHILOX>(x, rows, cols, rs, cs, vec_ok, signs, base, unit, amax, R, C, row, col, st);
     return launch_status("nvfp4_quantize_tile");
 }
 
@@ -355,6 +357,7 @@ struct __align__(128) StreamSmem {
 
 struct StreamArgs {
     const float* signs;
+    const float* amax;    // nullable: tensor amax left on the device by the producer of the source
     const int32_t* seed_base;
     int* status;          // nullable device int, raised when a bounded wait gave up
     Orient R, C;
@@ -526,8 +529,9 @@ quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_con
 #pragma unroll
         for (int l = 0; l < 16; ++l) sg[l] = a.signs ? __ldg(a.signs + l) : 1.f;
         ScaleMath sm_r{1.f, true}, sm_c{1.f, true};
-        if constexpr (ROW) sm_r = scale_math(__ldg(a.R.pts));
-        if constexpr (COL) sm_c = scale_math(__ldg(a.C.pts));
+        const bool writer = tid == 0 && blockIdx.x == 0;
+        if constexpr (ROW) sm_r = scale_math(tensor_scale(a.amax, a.R.pts, R_RHT, writer));
+        if constexpr (COL) sm_c = scale_math(tensor_scale(a.amax, a.C.pts, C_RHT, writer));
         if (sm_r.fast && sm_c.fast)
             stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, true>(S, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
         else
@@ -581,7 +585,8 @@ static cudaError_t launch_stream_sr(const CUtensorMap& mi, const CUtensorMap& mr
 
 // Returns NVFP4_ERR_UNSUPPORTED when the source does not qualify (the caller then uses the tile kernel).
 static int try_stream(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs, const float* signs,
-                      const int32_t* base, int* status, const Orient& R, const Orient& C, bool row, bool col, cudaStream_t st) {
+                      const float* amax, const int32_t* base, int* status, const Orient& R, const Orient& C, bool row, bool col,
+                      cudaStream_t st) {
     if (!stream_enabled() || (dtype != NVFP4_BF16 && dtype != NVFP4_F16) || cs != 1) return NVFP4_ERR_UNSUPPORTED;
     const int sr_mode = sr_of_flags(row ? R.flags : C.flags);
     if (dtype == NVFP4_F16 && sr_mode != SR_NONE) return NVFP4_ERR_UNSUPPORTED;          // FP16 sources are master weights
@@ -608,7 +613,7 @@ static int try_stream(const void* x, int dtype, int64_t rows, int64_t cols, int6
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    StreamArgs a{signs, base, status, R, C, static_cast<int>(rp / 128), static_cast<int>(cp / 128)};
+    StreamArgs a{signs, amax, base, status, R, C, static_cast<int>(rp / 128), static_cast<int>(cp / 128)};
     const int64_t tiles = static_cast<int64_t>(a.tiles_r) * a.tiles_c;
     const int grid = static_cast<int>(std::min<int64_t>(tiles, 2LL * sms));
     cudaError_t e;
@@ -714,9 +719,10 @@ extern "C" int nvfp4_amax(const void* x, int dtype, int64_t rows, int64_t cols, 
 }
 
 static int quantize_tile_impl(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs, const float* signs,
-                              const int32_t* seed_base, const float* unit, uint8_t* row_packed, uint8_t* row_scales,
-                              const float* row_pts, int row_flags, uint32_t row_seed, uint8_t* col_packed, uint8_t* col_scales,
-                              const float* col_pts, int col_flags, uint32_t col_seed, int* status, nvfp4_stream_t stream) {
+                              const int32_t* seed_base, const float* unit, const float* amax, uint8_t* row_packed,
+                              uint8_t* row_scales, float* row_pts, int row_flags, uint32_t row_seed, uint8_t* col_packed,
+                              uint8_t* col_scales, float* col_pts, int col_flags, uint32_t col_seed, int* status,
+                              nvfp4_stream_t stream) {
     NVFP4_REQUIRE(x, NVFP4_ERR_ARG, "nvfp4_quantize_tile: null source");
     NVFP4_REQUIRE(signs || !((row_flags | col_flags) & NVFP4_Q_RHT), NVFP4_ERR_ARG, "nvfp4_quantize_tile: the Hadamard transform needs the sign vector");
     NVFP4_REQUIRE(rows > 0 && cols > 0 && rs >= 0 && cs >= 0, NVFP4_ERR_ARG,
@@ -740,17 +746,17 @@ static int quantize_tile_impl(const void* x, int dtype, int64_t rows, int64_t co
     Orient R{row_packed, row_scales, row_pts, cp, row_seed, row_flags};
     Orient C{col_packed, col_scales, col_pts, rp, col_seed, col_flags};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const int rc = try_stream(x, dtype, rows, cols, rs, cs, signs, seed_base, status, R, C, row, col, st);
+    const int rc = try_stream(x, dtype, rows, cols, rs, cs, signs, amax, seed_base, status, R, C, row, col, st);
     if (rc != NVFP4_ERR_UNSUPPORTED) return rc;
     const int esz = dtype == NVFP4_F32 ? 4 : dtype == NVFP4_E4M3 ? 1 : 2;
     int vec_ok = cs == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (rs * esz) % 16 == 0;
     if (dtype == NVFP4_E4M3) {
         NVFP4_REQUIRE(cs == 1 && rs == cols, NVFP4_ERR_ARG, "nvfp4_quantize_fp8_weight: the weight must be contiguous");
-        return launch_tile<NVFP4_E4M3>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+        return launch_tile<NVFP4_E4M3>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, amax, R, C, row, col, st);
     }
-    if (dtype == NVFP4_F32) return launch_tile<NVFP4_F32>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
-    if (dtype == NVFP4_BF16) return launch_tile<NVFP4_BF16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
-    return launch_tile<NVFP4_F16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, R, C, row, col, st);
+    if (dtype == NVFP4_F32) return launch_tile<NVFP4_F32>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, amax, R, C, row, col, st);
+    if (dtype == NVFP4_BF16) return launch_tile<NVFP4_BF16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, amax, R, C, row, col, st);
+    return launch_tile<NVFP4_F16>(x, rows, cols, rs, cs, vec_ok, signs, seed_base, unit, amax, R, C, row, col, st);
 }
 
 extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
@@ -759,8 +765,20 @@ extern "C" int nvfp4_quantize_tile(const void* x, int dtype, int64_t rows, int64
                                    uint8_t* col_packed, uint8_t* col_scales, const float* col_pts, int col_flags,
                                    uint32_t col_seed, int* status, nvfp4_stream_t stream) {
     NVFP4_REQUIRE(dtype != NVFP4_E4M3, NVFP4_ERR_DTYPE, "nvfp4_quantize_tile: E4M3 weights go through nvfp4_quantize_fp8_weight");
-    return quantize_tile_impl(x, dtype, rows, cols, rs, cs, signs, seed_base, nullptr, row_packed, row_scales, row_pts, row_flags,
-                              row_seed, col_packed, col_scales, col_pts, col_flags, col_seed, status, stream);
+    return quantize_tile_impl(x, dtype, rows, cols, rs, cs, signs, seed_base, nullptr, nullptr, row_packed, row_scales,
+                              const_cast<float*>(row_pts), row_flags, row_seed, col_packed, col_scales, const_cast<float*>(col_pts),
+                              col_flags, col_seed, status, stream);
+}
+
+extern "C" int nvfp4_quantize_tile_amax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+                                        const float* signs, const int32_t* seed_base, const float* amax, uint8_t* row_packed,
+                                        uint8_t* row_scales, float* row_pts, int row_flags, uint32_t row_seed,
+                                        uint8_t* col_packed, uint8_t* col_scales, float* col_pts, int col_flags,
+                                        uint32_t col_seed, int* status, nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(dtype != NVFP4_E4M3, NVFP4_ERR_DTYPE, "nvfp4_quantize_tile_amax: E4M3 weights go through nvfp4_quantize_fp8_weight");
+    NVFP4_REQUIRE(amax, NVFP4_ERR_ARG, "nvfp4_quantize_tile_amax: null amax");
+    return quantize_tile_impl(x, dtype, rows, cols, rs, cs, signs, seed_base, nullptr, amax, row_packed, row_scales, row_pts,
+                              row_flags, row_seed, col_packed, col_scales, col_pts, col_flags, col_seed, status, stream);
 }
 
 extern "C" int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, int64_t rows, int64_t cols, const float* pts,
@@ -768,8 +786,8 @@ extern "C" int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, in
                                          nvfp4_stream_t stream) {
     NVFP4_REQUIRE(w && unit && pts, NVFP4_ERR_ARG, "nvfp4_quantize_fp8_weight: null pointer");
     // no sign vector: this path has no Hadamard transform (every pointer a kernel receives must be a device address)
-    return quantize_tile_impl(w, NVFP4_E4M3, rows, cols, cols, 1, nullptr, nullptr, unit, row_packed, row_scales, pts, 0, 0,
-                              col_packed, col_scales, pts, 0, 0, nullptr, stream);
+    return quantize_tile_impl(w, NVFP4_E4M3, rows, cols, cols, 1, nullptr, nullptr, unit, nullptr, row_packed, row_scales,
+                              const_cast<float*>(pts), 0, 0, col_packed, col_scales, const_cast<float*>(pts), 0, 0, nullptr, stream);
 }
 
 extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp,

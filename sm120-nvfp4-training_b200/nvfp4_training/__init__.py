@@ -47,10 +47,11 @@ def capture_frozen(model, compute, *inputs, backward=True, warmup=2):
     return capture(model, compute, *inputs, backward=backward, warmup=warmup)
 
 
-def enable_data_parallel(model, process_group=None, *, bucket_mb=None):
-    """Data-parallel replicas: bucketed NCCL all-reduce of the weight gradients, overlapped with backward."""
+def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2):
+    """Data-parallel replicas: NCCL all-reduce of the gradients, overlapped with backward.  Weight gradients of converted
+    layers are reduced in place, one collective each; small dense gradients share FP32 buckets of bucket_mb megabytes."""
     from .distributed import enable_data_parallel as enable
-    return enable(model, process_group, bucket_mb=bucket_mb)
+    return enable(model, process_group, bucket_mb=bucket_mb, depth=depth)
 
 
 def prepare_training(model, *, profile="balanced", precision="fp4", remat=False, lr=1e-4, betas=(0.9, 0.999), eps=1e-8,

@@ -27,6 +27,16 @@ def decoded(w: torch.Tensor) -> torch.Tensor:
     return (flat * scale).bfloat16().view(w.shape)
 
 
+def _flat(t: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """2-D view of an activation or gradient; an amax its producer left on the device stays attached to the view."""
+    flat = t.reshape(rows, cols)
+    if flat is not t:
+        hint = quant.known_amax(t)
+        if hint is not None and flat.data_ptr() == t.data_ptr():
+            quant.attach_amax(flat, hint)
+    return flat
+
+
 def _cached_scale(w: torch.Tensor):
     graph_scale = getattr(w, "_v5_graph_scale", None)
     if graph_scale is not None:
@@ -70,7 +80,7 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, signs, need_x, need_w, need_bias, save_packed):
         original_shape = tuple(x.shape)
-        x2 = x.reshape(-1, x.shape[-1])
+        x2 = _flat(x, -1, x.shape[-1])
         m, k = x2.shape
         n = w.shape[0]
         pts = _cached_scale(w)
@@ -131,7 +141,7 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, grad):
         saved = ctx.saved_tensors
         w, wpts, signs = saved[:3]
-        g = grad.reshape(ctx.m, ctx.n)
+        g = _flat(grad, ctx.m, ctx.n)
         if any(s == 0 for s in g.stride()):
             g = g.contiguous()
         dx = dw = db = None

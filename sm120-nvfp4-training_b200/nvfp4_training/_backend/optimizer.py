@@ -180,6 +180,7 @@ class AdamW(torch.optim.Optimizer):
         if any(not p.is_contiguous() or p.grad.is_sparse or not p.grad.is_contiguous() for p, g in active):
             raise ValueError('Dense contiguous parameters and gradients required')
         if self.reducer is not None:
+            self.reducer.begin([p for p, _ in active])     # an eager step: nothing is streamed, every collective is waited for
             self.reducer.reduce_dense([p for p, _ in active])
         for p, g in active:
             self._update_param(p, g)
@@ -219,7 +220,9 @@ class AdamW(torch.optim.Optimizer):
                     or not p.is_contiguous() or (p.grad is not None and (p.grad.is_sparse or not p.grad.is_contiguous()))):
                 raise ValueError("Expected contiguous CUDA FP32 parameters and dense gradients")
         if reducer is not None:
-            reducer.finish([p for p, _ in active if p not in pending])
+            # every gradient autograd left in .grad, also the second gradient of a parameter whose first one sits in a
+            # reducer slot (a weight shared with an embedding, a layer applied twice)
+            reducer.finish([p for p, _ in active])
         if audit:
             checks = [torch.isfinite(p.grad).all() for p, _ in active if p.grad is not None]
             checks.extend(torch.isfinite(t).all() for pack in pending.values() for t in pack if torch.is_tensor(t))
@@ -232,12 +235,15 @@ class AdamW(torch.optim.Optimizer):
     def _finish_streamed(self, p, group, pack, held, work=None):
         """Update p from a gradient whose all-reduce has completed (stream-wise)."""
         grad = held.pop(p, None)
-        if pack is not None and pack[1] is None and pack[2] is None and grad is not None and pack[0] is grad:
-            p.grad = grad                     # dense leaf gradient: the ordinary path reads p.grad
+        deferred = pack is not None and (pack[1] is not None or self.reducer.has_slot(p))
+        if not deferred:
+            # dense leaf gradient (reduced in place, or a view of a reduced bucket): the ordinary path reads p.grad
+            p.grad = pack[0] if pack is not None else grad
             self._update_overlapped(p, group, None, work)
-            p.grad = None
         else:
+            p.grad = grad      # None, or a second gradient beside the deferred one: the update adds it in FP32
             self._update_overlapped(p, group, pack, work)
+        p.grad = None
 
     def capture_streaming_backward(self, loss):
         """Record parameter-local updates once, as soon as each parameter's gradient is complete, inside backward
@@ -266,8 +272,9 @@ class AdamW(torch.optim.Optimizer):
                     else:
                         held[p] = p.grad          # keep the leaf gradient alive until its collective is consumed
                         p.grad = None
+                        both = pack is not None and held[p] is not None
                         for q, gq, packq, work in reducer.submit(p, group, pack if pack is not None else (held[p], None, None),
-                                                                 wait=False):
+                                                                 wait=False, extra=held[p] if both else None):
                             self._finish_streamed(q, gq, packq, held, work)
                 completed.add(p)
             return update

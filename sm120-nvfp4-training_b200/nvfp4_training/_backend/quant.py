@@ -120,6 +120,20 @@ def quantize(x: torch.Tensor, *, sr: bool = False, rht: bool = False, signs: Opt
     return Packed(d, s, p, x.dtype)
 
 
+def attach_amax(x: torch.Tensor, amax4: torch.Tensor) -> torch.Tensor:
+    """Mark x as produced by a kernel that left max |x| in amax4[0] (device float32[4], the layout of nat.amax); the
+    quantiser then needs no pass of its own over x and fills amax4[1], amax4[2] with the tensor scales."""
+    x._nvfp4_amax = (x._version, x.data_ptr(), amax4)
+    return x
+
+
+def known_amax(x: torch.Tensor):
+    hint = getattr(x, "_nvfp4_amax", None)
+    if hint is not None and hint[0] == x._version and hint[1] == x.data_ptr():
+        return hint[2]
+    return None
+
+
 def supported(x: torch.Tensor) -> bool:
     m, n = x.shape
     return m > 0 and n > 0 and min(x.stride()) >= 0
@@ -146,7 +160,8 @@ def dual(x: torch.Tensor, signs: torch.Tensor, *, sr: bool = False, clock=None, 
             return hit[2]
     d, s = _buffers(mp, np_, x.device)
     dt, st = _buffers(np_, mp, x.device)
-    scales = nat.amax(x)
+    produced = known_amax(x)
+    scales = produced if produced is not None else nat.amax(x)
     q, qt = scales[1], scales[2]
     if offset is None:
         offset = 0
@@ -162,7 +177,8 @@ def dual(x: torch.Tensor, signs: torch.Tensor, *, sr: bool = False, clock=None, 
         offset = offset + _RANK_OFFSET
     nat.quantize_tile(x, signs, row=dict(packed=d, scales=s, pts=q, flags=flag, seed=offset),
                       col=dict(packed=dt, scales=st, pts=qt, flags=flag | nat.Q_RHT, seed=offset + 1),
-                      seed_base=clock.seed if (clock is not None and sr) else None)
+                      seed_base=clock.seed if (clock is not None and sr) else None,
+                      amax=scales[0:1] if produced is not None else None)
     _STATS["quant"] += 2
     _STATS["rht_quant"] += 1
     _STATS["sr_quant"] += int(sr) * 2

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "nvfp4_amax_scratch_bytes": (I64, []),
     "nvfp4_amax": (I32, [P, I32, I64, I64, I64, I64, P, P, P]),
     "nvfp4_quantize_tile": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P, P]),
+    "nvfp4_quantize_tile_amax": (I32, [P, I32, I64, I64, I64, I64, P, P, P, P, P, P, I32, U32, P, P, P, I32, U32, P, P]),
     "nvfp4_quantize_fp8_weight": (I32, [P, P, I64, I64, P, P, P, P, P, P]),
     "nvfp4_quantize": (I32, [P, I32, I64, I64, I64, I64, I64, I64, I32, I32, U32, P, P, P, I32, P, P, P, P, P, P, P, P]),
     "nvfp4_quantize_static_max_elements": (I64, []),
@@ -38,8 +39,11 @@ _SIGNATURES = {
                                  F, F, F, F, F, F, F, U32, U32, P, P, P, P]),
     "nvfp4_adamw_plain": (I32, [P, P, P, P, I64, F, F, F, F, F, F, F, F, P, P]),
     "nvfp4_split_init": (I32, [P, I64, I32, P, P, P]),
-    "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I32, P]),
-    "nvfp4_swiglu": (I32, [P, P, P, P, P, I64, P]),
+    "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I64, I32, P, P]),
+    "nvfp4_swiglu": (I32, [P, I64, P, I64, P, I64, P, I64, P, I64, I64, I64, P, P]),
+    "nvfp4_add_rmsnorm": (I32, [P, P, P, F, I64, I64, P, P, P, P, P]),
+    "nvfp4_rmsnorm_bwd_partials": (I64, [I64, I64]),
+    "nvfp4_rmsnorm_bwd": (I32, [P, P, P, P, P, I64, I64, P, P, P, P, P]),
     "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
     "nvfp4_comfy_quantize": (I32, [P, I64, I64, P, I32, U32, P, P, P, P, P, P]),
     "nvfp4_comfy_dequantize": (I32, [P, P, P, P, I64, I64, P]),
@@ -125,8 +129,9 @@ def amax(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def quantize_tile(x, signs, *, row=None, col=None, seed_base=None):
-    """row / col: None or dict(packed, scales, pts, flags, seed)."""
+def quantize_tile(x, signs, *, row=None, col=None, seed_base=None, amax=None):
+    """row / col: None or dict(packed, scales, pts, flags, seed).  amax: device float left by the producer of x; the
+    kernel then computes the tensor scales itself and writes them into the pts tensors."""
     def unpack(o):
         if o is None:
             return None, None, None, 0, 0
@@ -134,6 +139,11 @@ def quantize_tile(x, signs, *, row=None, col=None, seed_base=None):
     rp, rs, rq, rf, rsd = unpack(row)
     cp, cs, cq, cf, csd = unpack(col)
     with torch.cuda.device(x.device):
+        if amax is not None:
+            check(lib().nvfp4_quantize_tile_amax(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1),
+                                                 signs.data_ptr(), ptr(seed_base), amax.data_ptr(), rp, rs, rq, rf, rsd, cp, cs, cq,
+                                                 cf, csd, status_word(x.device).data_ptr(), stream_of(x)))
+            return
         check(lib().nvfp4_quantize_tile(x.data_ptr(), dtype_code(x), x.shape[0], x.shape[1], x.stride(0), x.stride(1),
                                         signs.data_ptr(), ptr(seed_base), rp, rs, rq, rf, rsd, cp, cs, cq, cf, csd,
                                         status_word(x.device).data_ptr(), stream_of(x)))

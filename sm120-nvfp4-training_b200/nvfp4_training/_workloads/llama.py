@@ -1,6 +1,12 @@
 """Llama-style decoder used as the synthetic full-parameter training workload: RMSNorm, rotary positions, SwiGLU feed
 forward, causal attention through PyTorch's fused SDPA (attention stays BF16, as in the reference's workloads,
-src/nvfp4_training/_workloads/lm.py:20), untied embedding and head.  Every nn.Linear is converted by enable_nvfp4."""
+src/nvfp4_training/_workloads/lm.py:20), untied embedding and head.  Every nn.Linear is converted by enable_nvfp4.
+
+The q / k / v projections are one Linear of 3 * dim outputs and gate / up one Linear of 2 * ffn outputs (same parameters
+and arithmetic as separate layers, one tensor scale per fused weight), and the residual stream is carried as a pair
+(x, delta) whose sum is formed inside the next normalisation kernel.  On CUDA with BF16 activations the element-wise work
+runs on this library's fused kernels (_workloads/fused.py); `reference=True`, CPU tensors and other dtypes take plain
+PyTorch operations with the same mathematics (the check of the fused path in the tests)."""
 from __future__ import annotations
 
 import torch
@@ -30,39 +36,47 @@ def apply_rotary(x, cos, sin):
     return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1)
 
 
+def _fused_ok(x, reference):
+    return not reference and x.is_cuda and x.dtype == torch.bfloat16
+
+
 class Block(nn.Module):
-    def __init__(self, dim, heads, ffn):
+    def __init__(self, dim, heads, ffn, reference=False):
         super().__init__()
-        self.heads = heads
+        self.heads, self.reference = heads, reference
         self.norm1, self.norm2 = RMSNorm(dim), RMSNorm(dim)
-        self.q, self.k, self.v, self.o = (nn.Linear(dim, dim, bias=False) for _ in range(4))
-        self.gate, self.up = nn.Linear(dim, ffn, bias=False), nn.Linear(dim, ffn, bias=False)
+        self.qkv = nn.Linear(dim, 3 * dim, bias=False)
+        self.o = nn.Linear(dim, dim, bias=False)
+        self.gate_up = nn.Linear(dim, 2 * ffn, bias=False)
         self.down = nn.Linear(ffn, dim, bias=False)
 
-    def forward(self, x, cos, sin):
+    def forward(self, x, delta, cos, sin):
+        """The residual stream enters as x + delta (delta None for the first block) and leaves the same way."""
         b, s, d = x.shape
-        h = self.norm1(x)
-        q, k, v = (f(h).view(b, s, self.heads, d // self.heads) for f in (self.q, self.k, self.v))
-        if x.is_cuda and x.dtype == torch.bfloat16:
-            from .fused import rope, swiglu
-            q, k = rope(q, cos[:s], sin[:s]), rope(k, cos[:s], sin[:s])
-        else:
-            swiglu = lambda g, u: F.silu(g) * u
-            q, k = (apply_rotary(t.transpose(1, 2), cos, sin).transpose(1, 2) for t in (q, k))
-        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        if _fused_ok(x, self.reference):
+            from .fused import add_rmsnorm, rope_attention, swiglu
+            x, h = add_rmsnorm(x, delta, self.norm1.weight, self.norm1.eps)
+            attn = self.o(rope_attention(self.qkv(h), cos, sin, self.heads))
+            x, h = add_rmsnorm(x, attn, self.norm2.weight, self.norm2.eps)
+            return x, self.down(swiglu(self.gate_up(h)))
+        if delta is not None:
+            x = x + delta
+        q, k, v = (t.view(b, s, self.heads, d // self.heads).transpose(1, 2) for t in self.qkv(self.norm1(x)).split(d, dim=-1))
+        q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.o(a.transpose(1, 2).reshape(b, s, d))
-        h = self.norm2(x)
-        return x + self.down(swiglu(self.gate(h), self.up(h)))
+        gate, up = self.gate_up(self.norm2(x)).chunk(2, dim=-1)
+        return x, self.down(F.silu(gate) * up)
 
 
 class Decoder(nn.Module):
-    def __init__(self, *, layers=32, dim=3072, heads=24, ffn=8192, vocab=32000, seq=2048, std=0.02):
+    def __init__(self, *, layers=32, dim=3072, heads=24, ffn=8192, vocab=32000, seq=2048, std=0.02, reference=False):
         super().__init__()
         self.embed = nn.Embedding(vocab, dim)
-        self.blocks = nn.ModuleList(Block(dim, heads, ffn) for _ in range(layers))
+        self.blocks = nn.ModuleList(Block(dim, heads, ffn, reference) for _ in range(layers))
         self.norm = RMSNorm(dim)
         self.head = nn.Linear(dim, vocab, bias=False)
-        self.seq, self.head_dim = seq, dim // heads
+        self.seq, self.head_dim, self.reference = seq, dim // heads, reference
         for p in self.parameters():
             if p.ndim == 2:
                 nn.init.normal_(p, 0.0, std)
@@ -73,10 +87,13 @@ class Decoder(nn.Module):
         if self._tables is None or self._tables[0].shape[0] < s or self._tables[0].device != ids.device:
             self._tables = rotary_tables(max(s, self.seq), self.head_dim, ids.device)
         cos, sin = (t[:s].contiguous() for t in self._tables)
-        x = self.embed(ids).to(torch.bfloat16)
+        x, delta = self.embed(ids).to(torch.bfloat16), None
         for block in self.blocks:
-            x = block(x, cos, sin)
-        return self.head(self.norm(x))
+            x, delta = block(x, delta, cos, sin)
+        if _fused_ok(x, self.reference):
+            from .fused import add_rmsnorm
+            return self.head(add_rmsnorm(x, delta, self.norm.weight, self.norm.eps)[1])
+        return self.head(self.norm(x if delta is None else x + delta))
 
 
 def warm_attention(model, batch, seq, device):
@@ -84,8 +101,9 @@ def warm_attention(model, batch, seq, device):
     cuBLAS) create handles, plans and workspaces on first use, in the calling thread and in autograd's worker thread;
     that must happen before a CUDA-graph capture."""
     heads = model.blocks[0].heads
-    q, k, v = (torch.randn(batch, heads, seq, model.head_dim, device=device, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
-    F.scaled_dot_product_attention(q, k, v, is_causal=True).float().sum().backward()
+    qkv = torch.randn(batch, seq, 3, heads, model.head_dim, device=device, dtype=torch.bfloat16)
+    q, k, v = (qkv[:, :, i].detach().requires_grad_(True) for i in range(3))
+    F.scaled_dot_product_attention(*(t.transpose(1, 2) for t in (q, k, v)), is_causal=True).float().sum().backward()
     h = torch.randn(batch * seq, 64, device=device, dtype=torch.bfloat16, requires_grad=True)
     F.cross_entropy((h @ h.t()[:, :128]).float(), torch.zeros(batch * seq, dtype=torch.long, device=device)).backward()
     torch.cuda.synchronize(device)

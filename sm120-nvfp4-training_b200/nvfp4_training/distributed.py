@@ -6,7 +6,8 @@ The reference is single-GPU; this module is new.  Design:
   * a slot is all-reduced asynchronously as soon as its layer's backward has produced it, in backward order, so the
     transfer overlaps the remaining backward compute (NCCL runs on its own stream; only the consumer waits);
   * the fused AdamW kernel reads the reduced slot in place and folds the 1/world_size into its gradient decode;
-  * gradients that autograd leaves in .grad (norm gains, biases, embeddings) are reduced the same way in FP32;
+  * gradients that autograd leaves in .grad are reduced in FP32: large ones (embeddings) on their own, small ones (norm
+    gains, biases) packed into buckets of `bucket_mb` megabytes, one collective per bucket;
   * stochastic-rounding seeds of gradient quantisation get a per-rank offset; weights are re-quantised locally and are
     identical on all ranks because weights, rounding keys and step numbers are.
 Works eagerly and under CUDA-graph capture (the update of a parameter is deferred by `depth` parameters so that its
@@ -21,7 +22,7 @@ import torch.distributed as dist
 
 
 class GradientReducer:
-    def __init__(self, params, process_group=None, *, slot_dtype=torch.bfloat16, depth=2, owner_filter=None):
+    def __init__(self, params, process_group=None, *, slot_dtype=torch.bfloat16, depth=2, owner_filter=None, bucket_mb=25.0):
         self.group = process_group
         self.world = dist.get_world_size(process_group)
         self.rank = dist.get_rank(process_group)
@@ -35,6 +36,11 @@ class GradientReducer:
         self._works = []          # eager mode: outstanding collectives
         self._queue = deque()     # capture / streaming mode: (param, group, pack, work) waiting for their collective
         self.launched = []        # order in which slots were reduced (introspection / tests)
+        self._streaming = False   # True between begin(capturing=True) and the next begin()
+        self.bucket_bytes = int(float(bucket_mb or 0) * 2 ** 20)
+        self._bucket = []         # (param, group, gradient) of small dense gradients waiting for a shared collective
+        self._bucket_fill = 0
+        self.collectives = 0      # collectives started since begin()
 
     # ---- used by the linear layer's backward ------------------------------------------------------------
     def has_slot(self, p) -> bool:
@@ -56,6 +62,9 @@ class GradientReducer:
         self._works.clear()
         self._queue.clear()
         self.launched.clear()
+        self._bucket.clear()
+        self._bucket_fill = 0
+        self.collectives = 0
 
     def finish(self, dense_params):
         """Reduce the gradients autograd left in .grad, then wait (stream-wise) for every collective."""
@@ -65,44 +74,90 @@ class GradientReducer:
         self._works.clear()
 
     def reduce_dense(self, params):
+        """All-reduce the gradients autograd left in .grad and wait for them (stream-wise)."""
         for p in params:
             if p.grad is not None:
                 self._works.append(dist.all_reduce(p.grad, group=self.group, async_op=True))
-        if not getattr(self, "_streaming", False):
-            for work in self._works:
-                work.wait()
-            self._works.clear()
+        for work in self._works:
+            work.wait()
+        self._works.clear()
 
     # ---- streaming protocol (updates inside backward, eager or captured) ------------------------------
-    def submit(self, p, group, pack, wait=True):
+    def submit(self, p, group, pack, wait=True, extra=None):
         """Start the collective for p's gradient and return the (param, group, pack) items whose collectives have had
         `depth` later submissions to overlap with; those are safe to update now (after a stream-level wait).
         wait=False leaves that wait to the caller, who gets (param, group, pack, work) and may place it on the stream
-        its update runs on, so that the calling stream never waits for a collective."""
+        its update runs on, so that the calling stream never waits for a collective.
+        extra: a second gradient of the same parameter that autograd left in .grad (a weight shared with an embedding, a
+        layer applied twice); it is reduced as well and the returned work waits for both.
+        A dense gradient of at most a quarter of a bucket joins the open bucket instead of getting its own collective."""
         tensor = pack[0] if pack is not None else p.grad
+        dense = pack is None or (pack[1] is None and pack[2] is None and not self.has_slot(p))
+        nbytes = tensor.numel() * 4
+        if dense and extra is None and self.bucket_bytes and nbytes * 4 <= self.bucket_bytes:
+            self._bucket.append((p, group, tensor))
+            self._bucket_fill += nbytes
+            self.launched.append(p)
+            if self._bucket_fill >= self.bucket_bytes:
+                self._flush_bucket()
+            return self._pop(self.depth, wait)
         work = dist.all_reduce(tensor, group=self.group, async_op=True)
+        self.collectives += 1
+        if extra is not None:
+            work = _Both(work, dist.all_reduce(extra, group=self.group, async_op=True))
+            self.collectives += 1
         self.launched.append(p)
-        self._queue.append((p, group, pack, work))
+        self._queue.append(([(p, group, pack)], work))
         return self._pop(self.depth, wait)
 
+    def _flush_bucket(self):
+        """One FP32 buffer, one collective; the members' gradients become views of the reduced buffer."""
+        if not self._bucket:
+            return
+        flat = torch.cat([t.reshape(-1).float() for _, _, t in self._bucket])
+        work = dist.all_reduce(flat, group=self.group, async_op=True)
+        self.collectives += 1
+        items, at = [], 0
+        for p, group, t in self._bucket:
+            items.append((p, group, (flat[at:at + t.numel()].view(t.shape), None, None)))
+            at += t.numel()
+        self._queue.append((items, work))
+        self._bucket.clear()
+        self._bucket_fill = 0
+
     def drain(self, wait=True):
+        self._flush_bucket()
         return self._pop(0, wait)
 
     def _pop(self, keep, wait):
         ready = []
         while len(self._queue) > keep:
-            q, g, k, w = self._queue.popleft()
+            items, w = self._queue.popleft()
             if wait:
                 w.wait()
-                ready.append((q, g, k))
+                ready.extend(items)
             else:
-                ready.append((q, g, k, w))
+                ready.extend((q, g, k, w) for q, g, k in items)
         return ready
 
 
-def enable_data_parallel(model, process_group=None, *, bucket_mb=None, depth=2):
-    """Attach a GradientReducer to model.nvfp4_optimizer.  Call after enable_nvfp4 on every rank with identical
-    initial weights (same seed); the process group defaults to the world group."""
+class _Both:
+    """Two collectives that one update waits for."""
+
+    def __init__(self, first, second):
+        self.first, self.second = first, second
+
+    def wait(self):
+        self.first.wait()
+        self.second.wait()
+
+
+def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2):
+    """Attach a GradientReducer to model.nvfp4_optimizer.  Call after enable_nvfp4 on every rank; rank 0's weights are
+    broadcast.  The process group defaults to the world group.  depth: how many later gradients' collectives are started
+    before an update waits for its own (captured steps).  bucket_mb: small dense gradients (norm gains, biases) share
+    FP32 buckets of this size, one collective each; the weight gradients of converted layers are 19 MB and more each and
+    keep their own collective, written in place by the weight-gradient GEMM (0 gives every gradient its own)."""
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed must be initialised before enable_data_parallel")
     opt = model.nvfp4_optimizer
@@ -112,7 +167,7 @@ def enable_data_parallel(model, process_group=None, *, bucket_mb=None, depth=2):
         # collectives belong with the main line, or they would only run in its gaps and pile up behind backward.
         options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         process_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend="nccl", pg_options=options)
-    reducer = GradientReducer(params, process_group, depth=depth)
+    reducer = GradientReducer(params, process_group, depth=depth, bucket_mb=bucket_mb)
     opt.reducer = reducer
     from ._backend import quant
     quant._RANK_OFFSET = (reducer.rank * 0x9E3779B1) & 0xFFFFFFFF

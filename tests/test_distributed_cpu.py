@@ -27,7 +27,7 @@ def _worker(rank, world, port, results):
         for p in params[:3]:
             p._v4_request_scale = True       # "converted layer weights": gradients live in reducer slots
         index = {id(p): i for i, p in enumerate(params)}
-        red = GradientReducer(params, slot_dtype=torch.float32, depth=2)
+        red = GradientReducer(params, slot_dtype=torch.float32, depth=2, bucket_mb=0)
         assert red.world == world and red.grad_scale == 1.0 / world
         assert [red.has_slot(p) for p in params] == [True, True, True, False, False]
 
@@ -61,6 +61,36 @@ def _worker(rank, world, port, results):
         assert all(float(red.slot(p)[0]) == sum(range(world)) for p in params[:3])
         assert all(float(p.grad[0]) == sum(10.0 + r for r in range(world)) for p in params[3:])
         assert [index[id(p)] for p in red.launched] == [2, 1, 0]
+
+        # ---- buckets: small dense gradients share one FP32 collective, slot gradients keep their own -------------
+        red = GradientReducer(params, slot_dtype=torch.float32, depth=0, bucket_mb=1.0)
+        red.begin(params, capturing=True)
+        got = {}
+        for i, p in reversed(list(enumerate(params))):
+            if red.has_slot(p):
+                red.slot(p).fill_(float(rank + 1) * (i + 1))
+                pack = (red.slot(p), None, None)
+            else:
+                p.grad = torch.full_like(p, float(rank + 1) * (i + 1))
+                pack = (p.grad, None, None)
+            for q, _, k in red.submit(p, "group", pack):
+                got[index[id(q)]] = k[0].clone()
+        assert sorted(got) == [0, 1, 2]                      # the two dense gradients wait in the open bucket
+        for q, _, k in red.drain():
+            got[index[id(q)]] = k[0].clone()
+        assert red.collectives == 4                          # three slots + one bucket for parameters 3 and 4
+        assert all(got[i].shape == params[i].shape and abs(float(got[i].flatten()[0]) - total * (i + 1)) < 1e-6 for i in range(5))
+
+        # ---- a parameter with a slot gradient and a second dense gradient: both are reduced ----------------------
+        red.begin(params, capturing=True)
+        p0 = params[0]
+        red.slot(p0).fill_(float(rank + 1))
+        second = torch.full_like(p0, 10.0 * (rank + 1))
+        ready = red.submit(p0, "group", (red.slot(p0), None, None), extra=second) + red.drain()
+        assert len(ready) == 1 and float(red.slot(p0)[0]) == total and float(second[0]) == 10.0 * total
+        # an eager step after a captured one waits for its collectives again
+        red.begin(params)
+        assert red._streaming is False
         results[rank] = "ok"
     except Exception as e:  # pragma: no cover - reported to the parent
         results[rank] = repr(e)
