@@ -310,6 +310,96 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const uint4* __restric
     }
 }
 
+// The same backward pass with every thread owning CPT fixed groups of eight columns: the dgamma sums stay in registers,
+// four rows are in flight per thread (loads of all four are issued before the first is used) and each row is read once.
+// The row-wise dot products are combined through shared memory in a fixed order.  Used when the column count divides
+// evenly over the CTA; the warp-per-row kernel above serves the other shapes.
+template <int CPT>
+__global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ sum,
+                                                               const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                               const uint4* __restrict__ dres, int64_t rows, int chunks,
+                                                               uint4* __restrict__ dx, float* __restrict__ partial,
+                                                               float* __restrict__ amax_out) {
+    constexpr int R = 4;
+    __shared__ float dots[2][R][12];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+    float w[CPT][8], acc[CPT][8];
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+        const int c = tid + k * blockDim.x;
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c + 1);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { w[k][j] = bf16_value(bf16_bits(g[j])); acc[k][j] = 0.f; }
+    }
+    const float inv_d = 1.f / static_cast<float>(chunks * 8);
+    float best = 0.f;
+    int phase = 0;
+    for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * R; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * R, phase ^= 1) {
+        uint4 pg[R][CPT], ps[R][CPT];
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const int64_t at = (r0 + i) * chunks + tid + k * blockDim.x;
+                const bool live = r0 + i < rows;
+                pg[i][k] = live ? dh[at] : make_uint4(0, 0, 0, 0);
+                ps[i][k] = live ? sum[at] : make_uint4(0, 0, 0, 0);
+            }
+        float rs[R], dot[R];
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            rs[i] = r0 + i < rows ? rstd[r0 + i] : 0.f;
+            dot[i] = 0.f;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                float g[8], sv[8];
+                unpack8(pg[i][k], g); unpack8(ps[i][k], sv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    dot[i] = fmaf(g[j] * w[k][j], sv[j], dot[i]);
+                    acc[k][j] = fmaf(g[j] * sv[j], rs[i], acc[k][j]);
+                }
+            }
+            dot[i] = warp_sum(dot[i]);
+            if (lane == 0) dots[phase][i][warp] = dot[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            if (r0 + i >= rows) break;
+            float total = 0.f;
+            for (int q = 0; q < warps; ++q) total += dots[phase][i][q];
+            const float kf = rs[i] * rs[i] * rs[i] * inv_d * total;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const int64_t at = (r0 + i) * chunks + tid + k * blockDim.x;
+                float g[8], sv[8], o[8];
+                unpack8(pg[i][k], g); unpack8(ps[i][k], sv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = rs[i] * (g[j] * w[k][j]) - sv[j] * kf;
+                if (dres) {
+                    float d[8];
+                    unpack8(dres[at], d);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] += d[j];
+                }
+                const uint4 packed = pack8(o);
+                dx[at] = packed;
+                best = fmaxf(best, abs_max8(packed));
+            }
+        }
+    }
+    best = warp_max(best);
+    if (lane == 0) atomic_amax(amax_out, best);
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+        float* dst = partial + static_cast<size_t>(blockIdx.x) * chunks * 8 + static_cast<size_t>(tid + k * blockDim.x) * 8;
+        reinterpret_cast<float4*>(dst)[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+    }
+}
+
 __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int parts, int cols, float* __restrict__ out) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= cols) return;
@@ -347,7 +437,17 @@ extern "C" int nvfp4_add_rmsnorm(const void* x, const void* delta, const float* 
     return launch_status("nvfp4_add_rmsnorm");
 }
 
+// threads (a multiple of 32, at most 384) and column groups per thread (at most 2) of the column-owner kernel, or 0
+static int cols_threads(int64_t cols, int* cpt) {
+    const int64_t chunks = cols / 8;
+    for (int k = 1; k <= 2; ++k)
+        if (chunks % k == 0 && (chunks / k) % 32 == 0 && chunks / k <= 384) { *cpt = k; return static_cast<int>(chunks / k); }
+    return 0;
+}
+
 extern "C" int64_t nvfp4_rmsnorm_bwd_partials(int64_t rows, int64_t cols) {
+    int cpt = 0;
+    if (cols_threads(cols, &cpt)) return std::min<int64_t>((rows + 3) / 4, 148 * 2);
     const int warps = norm_warps(static_cast<int>(cols), 4);
     return std::min<int64_t>((rows + warps - 1) / warps, 148 * 2);
 }
@@ -368,6 +468,18 @@ extern "C" int nvfp4_rmsnorm_bwd(const void* dh, const void* sum, const float* r
     }
     const int parts = static_cast<int>(nvfp4_rmsnorm_bwd_partials(rows, cols));
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int cpt = 0;
+    if (const int threads = cols_threads(cols, &cpt)) {
+        auto launch = [&](auto kernel) {
+            kernel<<<parts, threads, 0, st>>>(static_cast<const uint4*>(dh), static_cast<const uint4*>(sum), rstd, gamma,
+                                             static_cast<const uint4*>(dres), rows, static_cast<int>(cols / 8), static_cast<uint4*>(dx),
+                                             partial, amax_out);
+        };
+        if (cpt == 1) launch(rmsnorm_bwd_cols_kernel<1>);
+        else launch(rmsnorm_bwd_cols_kernel<2>);
+        colsum_finish_kernel<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, st>>>(partial, parts, static_cast<int>(cols), dgamma);
+        return launch_status("nvfp4_rmsnorm_bwd");
+    }
     rmsnorm_bwd_kernel<<<parts, warps * 32, smem, st>>>(static_cast<const uint4*>(dh), static_cast<const uint4*>(sum), rstd, gamma,
                                                         static_cast<const uint4*>(dres), rows, static_cast<int>(cols / 8),
                                                         static_cast<uint4*>(dx), partial, amax_out);

@@ -30,10 +30,15 @@ _LAST_DUAL: dict = {}
 _MEMO_IN_CAPTURE = False
 
 
+_CAPTURE_EDGE_HOOKS = []   # callables run where a step capture begins and ends (pools that must not cross that edge)
+
+
 def remember_in_capture(on: bool) -> None:
     global _MEMO_IN_CAPTURE
     _MEMO_IN_CAPTURE = bool(on)
     _LAST_DUAL.clear()
+    for hook in _CAPTURE_EDGE_HOOKS:
+        hook()
 
 
 def sr_flag() -> int:

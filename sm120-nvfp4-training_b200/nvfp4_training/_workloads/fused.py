@@ -8,12 +8,30 @@ import torch
 from torch.nn import functional as F
 
 from .. import _native as nat
+from .._backend import quant as _quant
 from .._backend.quant import attach_amax
 
 
+_SLOTS = {}          # (device index, capturing) -> [zeroed float32 chunk, slots handed out]
+_SLOTS_PER_CHUNK = 256
+
+
 def _amax_slot(device):
-    """float32[4] in the layout of nat.amax: [0] receives the amax, the quantiser fills in the scales."""
-    return torch.zeros(4, dtype=torch.float32, device=device)
+    """float32[4] in the layout of nat.amax: [0] receives the amax, the quantiser fills in the scales.  Slots are cut from
+    chunks that are zeroed once (one fill kernel per 256 slots instead of one per slot).  A chunk made while a CUDA graph
+    is being captured lives in that graph's memory and is zeroed again by every replay; it is never handed out after
+    the capture has ended (forget_slots, called where captures begin and end)."""
+    key = (torch.device(device).index, torch.cuda.is_current_stream_capturing())
+    entry = _SLOTS.get(key)
+    if entry is None or entry[1] == _SLOTS_PER_CHUNK:
+        entry = _SLOTS[key] = [torch.zeros(4 * _SLOTS_PER_CHUNK, dtype=torch.float32, device=device), 0]
+    slot = entry[0][4 * entry[1]: 4 * entry[1] + 4]
+    entry[1] += 1
+    return slot
+
+
+def forget_slots():
+    _SLOTS.clear()
 
 
 def _run(fn, *args):
@@ -199,3 +217,6 @@ class _Rope(torch.autograd.Function):
 def rope(x, cos, sin):
     """x [B, S, H, D] BF16 -> rotated copy; cos / sin [S, D / 2] BF16 contiguous."""
     return _Rope.apply(x, cos, sin)
+
+
+_quant._CAPTURE_EDGE_HOOKS.append(forget_slots)

@@ -111,7 +111,7 @@ def warm_attention(model, batch, seq, device):
 
 def token_loss(model, ids, targets):
     logits = model(ids)
-    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.view(-1))
+    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
 
 
 def linear_parameters(model) -> int:

@@ -45,7 +45,7 @@ def test_swiglu_forward_backward_and_amax():
     assert known_amax(out)[0].item() == out.detach().abs().max().item()
     d = torch.randn_like(out)
     seen = {}
-    gu.register_hook(lambda grad: seen.setdefault("amax", known_amax(grad)))
+    gu.register_hook(lambda grad: seen.update(amax=known_amax(grad)))
     out.backward(d)
     ref.backward(d.float())
     assert torch.allclose(gu.grad.float(), ref_in.grad, atol=2e-2, rtol=2e-2)
@@ -65,10 +65,8 @@ def test_add_rmsnorm_forward_backward_and_amax(rows, cols, with_delta):
     xf = x.detach().float().requires_grad_(True)
     df = delta.detach().float().requires_grad_(True) if with_delta else None
     gf = gamma.detach().clone().requires_grad_(True)
-    tf = (xf + df).bfloat16().float() if with_delta else xf
-    if with_delta:
-        tf = xf + df   # differentiable path; the kernel's one extra rounding of the sum is inside the tolerance
-    hf = F.rms_norm(tf, (cols,), gf.bfloat16().float() + (gf - gf.detach()), 1e-5)
+    tf = xf + df if with_delta else xf   # the kernel's one extra rounding of the sum is inside the tolerance
+    hf = F.rms_norm(tf, (cols,), gf.detach().bfloat16().float() + (gf - gf.detach()), 1e-5)   # value bf16(gamma), gradient to gamma
     _close(total, tf)
     _close(h, hf)
     assert known_amax(h)[0].item() == h.detach().abs().max().item()
@@ -76,7 +74,7 @@ def test_add_rmsnorm_forward_backward_and_amax(rows, cols, with_delta):
     dh = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
     dt = (torch.randn(rows, cols, device="cuda", generator=g) * 0.3).bfloat16()
     seen = {}
-    x.register_hook(lambda grad: seen.setdefault("amax", known_amax(grad)))
+    x.register_hook(lambda grad: seen.update(amax=known_amax(grad)))
     torch.autograd.backward([h, total], [dh, dt])
     torch.autograd.backward([hf, tf], [dh.float(), dt.float()])
     _close(x.grad, xf.grad)
