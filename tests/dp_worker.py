@@ -39,10 +39,39 @@ def main():
     ref = flat.clone()
     dist.broadcast(ref, src=0)
     same = torch.equal(flat, ref)
-    ok = torch.tensor([int(same and losses[-1] < 0.8 * losses[0])], device=dev)
+    # a head tied to the embedding: the shared weight has a deferred NVFP4 gradient (the head) AND an autograd gradient
+    # (the embedding); both must be reduced or the replicas drift apart
+    class Tied(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embedding = nn.Embedding(256, 128)
+            self.mid = nn.Linear(128, 128)
+            self.head = nn.Linear(128, 256, bias=False)
+            self.head.weight = self.embedding.weight
+
+        def forward(self, tokens):
+            return self.head(F.gelu(self.mid(self.embedding(tokens))))
+
+    torch.manual_seed(300 + rank)
+    tied = nv.enable_nvfp4(Tied().to(dev), profile="balanced", lr=2e-3)
+    nv.enable_data_parallel(tied)
+
+    def ce(m, t, y):
+        return F.cross_entropy(m(t).flatten(0, 1).float(), y.flatten())
+
+    tok = torch.randint(0, 256, (2, 4, 64), device=dev, generator=g)
+    tied_losses = [nv.train_step(tied, ce, tok[0], tok[1]).item() for _ in range(6)]
+    with nv.capture_step(tied, ce, tok[0], tok[1], steps=6) as graph:
+        tied_losses += [graph.step(tok[0], tok[1]).item() for _ in range(6)]
+    tflat = torch.cat([p.detach().float().flatten() for p in tied.parameters()])
+    tref = tflat.clone()
+    dist.broadcast(tref, src=0)
+    same_tied = torch.equal(tflat, tref)
+    ok = torch.tensor([int(same and same_tied and losses[-1] < 0.8 * losses[0])], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"DP_RESULT ok={int(ok.item())} same={same} first={losses[0]:.4f} last={losses[-1]:.4f}", flush=True)
+        print(f"DP_RESULT ok={int(ok.item())} same={same} same_tied={same_tied} first={losses[0]:.4f} last={losses[-1]:.4f} "
+              f"tied_first={tied_losses[0]:.4f} tied_last={tied_losses[-1]:.4f}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if ok.item() else 1)
 

@@ -23,11 +23,13 @@ def test_list_profiles_cli():
     assert out == ["balanced", "short128", "conservative", "same_as_v5", "experimental_m4v4", "experimental_fp8_master"]
 
 
-def test_check_cli_one_profile(tmp_path):
+@pytest.mark.parametrize("profile", ["balanced", "experimental_fp8_master"])
+def test_check_cli_one_profile(tmp_path, profile):
     target = tmp_path / "check.json"
-    run("-m", "nvfp4_training", "check", "--profile", "balanced", "--output", str(target))
+    run("-m", "nvfp4_training", "check", "--profile", profile, "--output", str(target))
     report = json.loads(target.read_text())
     assert report["status"] == "passed" and len(report["cases"]) == 4 and all(c["exact_resume"] for c in report["cases"])
+    assert all((c["gemms"], c["sr"], c["rht"], c["final_step"]) == (9, 6, 6, 7) for c in report["cases"])
 
 
 def test_bench_cli_small(tmp_path):
