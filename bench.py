@@ -359,6 +359,7 @@ def run_train(args, rank, world, device):
     with torch.device(device):
         model = Decoder(layers=cfg["layers"], dim=cfg["dim"], heads=cfg["heads"], ffn=cfg["ffn"], vocab=cfg["vocab"], seq=cfg["seq"])
     model = nv.enable_nvfp4(model, profile="balanced", lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    model.nvfp4_optimizer.param_groups[0]["prepack"] = os.environ.get("NVFP4_PREPACK", "0") == "1"
     if world > 1:
         nv.enable_data_parallel(model)
     n_linear = linear_parameters(model)

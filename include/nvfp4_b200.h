@@ -200,6 +200,24 @@ int nvfp4_adamw_step(void* p, int master, const void* grad, int grad_kind, int64
                      const float* ctrl, float* scale_out, void* scratch, nvfp4_stream_t stream);
 
 /*
+ * nvfp4_adamw_step for a weight matrix [rows][cols] that ALSO writes the next forward's two weight packings in the same
+ * launch: after the update the kernel's CTAs meet at a grid barrier (cooperative launch, bounded wait, `status` as in
+ * nvfp4_gemm) and then quantise the updated master, still resident in L2, against the NEW tensor scale it has just
+ * published: packed / scales = the packing of W, packed_t / scales_t that of W^T, round to nearest, byte-identical to
+ * nvfp4_quantize(pair = 1) on the updated weight.  Masters FP16 / BF16 (+ tail) / FP32 with the moment formats of the
+ * profiles (FP8 masters are refused, as in the reference).  scratch as for nvfp4_adamw_step; scale_out is required.
+ * Replaces the FUSE path of adam_kernel.update (src/nvfp4_training/_backend/adam_kernel.py:196-202), whose packings are
+ * made with the previous scale and repaired afterwards by prepack._repair (prepack.py:7-37, read at linear6.py:41-55);
+ * here the packings are final when the kernel ends.
+ */
+int nvfp4_adamw_step_prepack(void* p, int master, const void* grad, int grad_kind, int64_t grad_cols, int64_t grad_stride,
+                             const float* sa, const float* sb, const float* extra, float grad_mul, void* m, void* v, float* ms,
+                             float* vs, int8_t* tail, int64_t rows, int64_t cols, int vbits, int mbits, int nonlinear_m,
+                             int state_block, float lr, float decay, float b1, float b2, float c1, float c2, float eps,
+                             uint32_t step, uint32_t key, const float* ctrl, float* scale_out, uint8_t* packed, uint8_t* scales,
+                             uint8_t* packed_t, uint8_t* scales_t, void* scratch, int* status, nvfp4_stream_t stream);
+
+/*
  * AdamW with FP32 master and FP32 moments for tensors below 4096 elements (norm gains, biases).
  * Replaces optimizer_v5._update with COMPACT = False (src/nvfp4_training/_backend/optimizer_v5.py:9-53).
  */

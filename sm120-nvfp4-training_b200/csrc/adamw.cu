@@ -14,9 +14,10 @@
 // Work split: a warp owns 512 consecutive elements, lane l the 16 elements [16 l, 16 l + 16).  State blocks
 // (512, 256, 128 or 64 elements) therefore cover 32, 16, 8 or 4 adjacent lanes and their maxima are plain
 // segmented shuffles: no shared memory, no block barrier on the data path.
-#include "common.cuh"
+#include "pack_tile.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace nvfp4 {
 
@@ -91,18 +92,15 @@ __device__ __forceinline__ void store16(T* base, int64_t i0, int64_t n, const T 
     }
 }
 
+// The update of one chunk of 4096 elements by a CTA of 256 threads; returns this lane's share of max |bf16(new weight)|.
 template <int MASTER, int VB, bool M4, bool NL, int B>
-__global__ void __launch_bounds__(256, 4) adamw_kernel(const AdamArgs a) {
+__device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, float c1, float c2, uint32_t step) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * 8 + warp) * 512 + lane * 16;
+    const int64_t i0 = (chunk * 8 + warp) * 512 + lane * 16;
     const int64_t n = a.n;
     const bool any = i0 < n;
     const int64_t blk = i0 / B;
     constexpr int LANES_B = B / 16;
-
-    float c1 = a.c1, c2 = a.c2;
-    uint32_t step = a.step;
-    if (a.ctrl) { c1 = a.ctrl[0]; c2 = a.ctrl[1]; step = __float_as_uint(a.ctrl[3]); }
     const float one_b1 = 1.f - a.b1, one_b2 = 1.f - a.b2, lrc1 = a.lr * c1;
 
     float p[16], g[16], m[16], v[16];
@@ -410,27 +408,82 @@ __global__ void __launch_bounds__(256, 4) adamw_kernel(const AdamArgs a) {
         store16(static_cast<uint16_t*>(a.v), i0, n, out);
         if (any && (lane & (LANES_B - 1)) == 0) a.vs[blk] = sc;
     }
-    // ---- tensor scale for the next forward: max(amax, 1e-12) * (1/2688) ----
-    if (a.scale_out) {
-        __shared__ float warp_amax[8];
-        __shared__ bool last;
-        amax = seg_max(amax, 32);
-        if (lane == 0) warp_amax[warp] = amax;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float b = 0.f;
-            for (int w = 0; w < 8; ++w) b = fmaxf(b, warp_amax[w]);
-            atomicMax(&a.scratch[0], __float_as_uint(b));  // non-negative floats order like their bit patterns
+    return amax;
+}
+
+// Tensor scale for the next forward, max(amax, 1e-12) * (1 / 2688): block maximum, one atomic per CTA, the last CTA to
+// arrive publishes the scale and leaves the two scratch words zeroed.
+__device__ __forceinline__ void adam_publish_scale(const AdamArgs& a, float amax) {
+    __shared__ float warp_amax[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    amax = seg_max(amax, 32);
+    if (lane == 0) warp_amax[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = 0.f;
+        for (int w = 0; w < 8; ++w) b = fmaxf(b, warp_amax[w]);
+        atomicMax(&a.scratch[0], __float_as_uint(b));  // non-negative floats order like their bit patterns
+        __threadfence();
+        if (atomicAdd(&a.scratch[1], 1u) == gridDim.x - 1) {
             __threadfence();
-            last = atomicAdd(&a.scratch[1], 1u) == gridDim.x - 1;
-            if (last) {
-                __threadfence();
-                const float total = __uint_as_float(atomicExch(&a.scratch[0], 0u));
-                a.scale_out[0] = fmaxf(total, 1.e-12f) * (1.f / 2688.f);
-                a.scratch[1] = 0u;
-            }
+            const float total = __uint_as_float(atomicExch(&a.scratch[0], 0u));
+            a.scale_out[0] = fmaxf(total, 1.e-12f) * (1.f / 2688.f);
+            a.scratch[1] = 0u;
         }
     }
+}
+
+template <int MASTER, int VB, bool M4, bool NL, int B>
+__global__ void __launch_bounds__(256, 4) adamw_kernel(const AdamArgs a) {
+    float c1 = a.c1, c2 = a.c2;
+    uint32_t step = a.step;
+    if (a.ctrl) { c1 = a.ctrl[0]; c2 = a.ctrl[1]; step = __float_as_uint(a.ctrl[3]); }
+    const float amax = adam_chunk<MASTER, VB, M4, NL, B>(a, blockIdx.x, c1, c2, step);
+    if (a.scale_out) adam_publish_scale(a, amax);
+}
+
+// The update AND the next forward's weight packings in one launch.  Phase 1: a grid of resident CTAs walks the chunks and
+// publishes the new tensor scale.  Grid barrier.  Phase 2: the same CTAs walk the 128 x 128 tiles of the updated weight
+// (still in L2: a weight is at most a few tens of megabytes) and write both NVFP4 orientations against the new scale,
+// byte-identical to quantising the updated weight in the next forward.
+// The barrier is an arrival counter in the caller's scratch; the launch asks for no more CTAs than fit the GPU at once
+// (cooperative launch), and the wait is bounded: on expiry the status word is raised and phase 2 is skipped.
+template <int MASTER, int VB, bool M4, bool NL, int B>
+__global__ void __launch_bounds__(256, 4) adamw_prepack_kernel(const AdamArgs a, const PackArgs k) {
+    __shared__ PackSmem pack;
+    __shared__ int proceed;
+    float c1 = a.c1, c2 = a.c2;
+    uint32_t step = a.step;
+    if (a.ctrl) { c1 = a.ctrl[0]; c2 = a.ctrl[1]; step = __float_as_uint(a.ctrl[3]); }
+    const int64_t chunks = (a.n + 4095) / 4096;
+    float amax = 0.f;
+    for (int64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x)
+        amax = fmaxf(amax, adam_chunk<MASTER, VB, M4, NL, B>(a, chunk, c1, c2, step));
+    adam_publish_scale(a, amax);
+    // ---- grid barrier: every CTA's master stores and the published scale are visible after it ----
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(k.barrier, 1u);
+        const long long t0 = clock64();
+        int ok = 1;
+        while (*reinterpret_cast<volatile unsigned int*>(k.barrier) < gridDim.x) {
+            __nanosleep(200);
+            if (clock64() - t0 > 4000000000LL) { ok = 0; break; }
+        }
+        __threadfence();
+        proceed = ok;
+        if (!ok && k.status) *k.status = NVFP4_ERR_TIMEOUT;
+    }
+    __syncthreads();
+    if (proceed) {
+        const float inv = __fdiv_rn(1.f, __ldcg(a.scale_out));
+        const int64_t tiles_c = round128(k.cols) / 128, tiles = (round128(k.rows) / 128) * tiles_c;
+        for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) pack_tile<MASTER>(a.p, k, t / tiles_c, t % tiles_c, inv, pack);
+    }
+    // the last CTA to leave zeroes the barrier word for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(k.barrier, 1u) == 2u * gridDim.x - 1u) *k.barrier = 0u;
 }
 
 // FP32 moments, FP32 master: tensors below 4096 elements (norm gains, biases).
@@ -476,32 +529,46 @@ static bool launch_master(const AdamArgs& a, int vbits, int mbits, int nl, int b
 
 using namespace nvfp4;
 
+static int fill_adam_args(AdamArgs& a, const char* who, void* p, int master, const void* grad, int grad_kind, int64_t grad_cols,
+                          int64_t grad_stride, const float* sa, const float* sb, const float* extra, float grad_mul, void* m, void* v,
+                          float* ms, float* vs, int8_t* tail, float* unit, int64_t n, int vbits, int mbits, int state_block, float lr,
+                          float decay, float b1, float b2, float c1, float c2, float eps, uint32_t step, uint32_t key,
+                          const float* ctrl, float* scale_out, void* scratch) {
+    NVFP4_REQUIRE(p && grad && m && ms && vs, NVFP4_ERR_ARG, "%s: null pointer", who);
+    NVFP4_REQUIRE(n > 0, NVFP4_ERR_ARG, "%s: empty tensor", who);
+    NVFP4_REQUIRE(master == 32 || master == 24 || master == 17 || master == 16 || master == 8, NVFP4_ERR_ARG,
+                  "%s: unknown master encoding %d", who, master);
+    NVFP4_REQUIRE(state_block == 512 || state_block == 256 || state_block == 128 || state_block == 64, NVFP4_ERR_ARG,
+                  "%s: state block must be 64, 128, 256 or 512", who);
+    NVFP4_REQUIRE(master != 8 || state_block == 512, NVFP4_ERR_ARG, "%s: FP8 masters use 512-element units", who);
+    NVFP4_REQUIRE(grad_kind >= 0 && grad_kind <= 2, NVFP4_ERR_ARG, "%s: unknown gradient kind %d", who, grad_kind);
+    NVFP4_REQUIRE(grad_kind != 2 || (sa && sb && grad_cols > 0 && grad_stride >= grad_cols), NVFP4_ERR_ARG,
+                  "%s: scaled raw gradients need both scales and a valid stride", who);
+    NVFP4_REQUIRE(master != 24 || tail, NVFP4_ERR_ARG, "%s: split masters need the tail tensor", who);
+    NVFP4_REQUIRE(master != 8 || unit, NVFP4_ERR_ARG, "%s: FP8 masters need the unit tensor", who);
+    NVFP4_REQUIRE(v || (mbits == 4 && vbits == 4), NVFP4_ERR_ARG, "%s: missing variance tensor", who);
+    NVFP4_REQUIRE(!scale_out || scratch, NVFP4_ERR_ARG, "%s: the amax reduction needs scratch", who);
+    a = AdamArgs{};
+    a.p = p; a.grad = grad; a.extra = extra; a.m = m; a.v = v; a.ms = ms; a.vs = vs; a.tail = tail; a.unit = unit;
+    a.sa = sa; a.sb = sb; a.ctrl = ctrl; a.scale_out = scale_out;
+    a.scratch = scratch ? reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + SCRATCH_ADAM_OFFSET) : nullptr;
+    a.n = n; a.grad_cols = grad_kind == 2 ? grad_cols : 1; a.grad_stride = grad_kind == 2 ? grad_stride : 1; a.grad_kind = grad_kind;
+    a.lr = lr; a.decay = decay; a.b1 = b1; a.b2 = b2; a.c1 = c1; a.c2 = c2; a.eps = eps; a.grad_mul = grad_mul;
+    a.step = step; a.key = key;
+    return NVFP4_OK;
+}
+
 extern "C" int nvfp4_adamw_step(void* p, int master, const void* grad, int grad_kind, int64_t grad_cols, int64_t grad_stride,
                                 const float* sa, const float* sb, const float* extra, float grad_mul, void* m, void* v,
                                 float* ms, float* vs, int8_t* tail, float* unit, int64_t n, int vbits, int mbits,
                                 int nonlinear_m, int state_block, float lr, float decay, float b1, float b2, float c1, float c2,
                                 float eps, uint32_t step, uint32_t key, const float* ctrl, float* scale_out, void* scratch,
                                 nvfp4_stream_t stream) {
-    NVFP4_REQUIRE(p && grad && m && ms && vs, NVFP4_ERR_ARG, "nvfp4_adamw_step: null pointer");
-    NVFP4_REQUIRE(n > 0, NVFP4_ERR_ARG, "nvfp4_adamw_step: empty tensor");
-    NVFP4_REQUIRE(master == 32 || master == 24 || master == 17 || master == 16 || master == 8, NVFP4_ERR_ARG,
-                  "nvfp4_adamw_step: unknown master encoding %d", master);
-    NVFP4_REQUIRE(state_block == 512 || state_block == 256 || state_block == 128 || state_block == 64, NVFP4_ERR_ARG,
-                  "nvfp4_adamw_step: state block must be 64, 128, 256 or 512");
-    NVFP4_REQUIRE(master != 8 || state_block == 512, NVFP4_ERR_ARG, "nvfp4_adamw_step: FP8 masters use 512-element units");
-    NVFP4_REQUIRE(grad_kind >= 0 && grad_kind <= 2, NVFP4_ERR_ARG, "nvfp4_adamw_step: unknown gradient kind %d", grad_kind);
-    NVFP4_REQUIRE(grad_kind != 2 || (sa && sb && grad_cols > 0 && grad_stride >= grad_cols), NVFP4_ERR_ARG,
-                  "nvfp4_adamw_step: scaled raw gradients need both scales and a valid stride");
-    NVFP4_REQUIRE(master != 24 || tail, NVFP4_ERR_ARG, "nvfp4_adamw_step: split masters need the tail tensor");
-    NVFP4_REQUIRE(master != 8 || unit, NVFP4_ERR_ARG, "nvfp4_adamw_step: FP8 masters need the unit tensor");
-    NVFP4_REQUIRE(v || (mbits == 4 && vbits == 4), NVFP4_ERR_ARG, "nvfp4_adamw_step: missing variance tensor");
-    NVFP4_REQUIRE(!scale_out || scratch, NVFP4_ERR_ARG, "nvfp4_adamw_step: the amax reduction needs scratch");
-    AdamArgs a{};
-    a.p = p; a.grad = grad; a.extra = extra; a.m = m; a.v = v; a.ms = ms; a.vs = vs; a.tail = tail; a.unit = unit;
-    a.sa = sa; a.sb = sb; a.ctrl = ctrl; a.scale_out = scale_out; a.scratch = scratch ? reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + SCRATCH_ADAM_OFFSET) : nullptr;
-    a.n = n; a.grad_cols = grad_kind == 2 ? grad_cols : 1; a.grad_stride = grad_kind == 2 ? grad_stride : 1; a.grad_kind = grad_kind;
-    a.lr = lr; a.decay = decay; a.b1 = b1; a.b2 = b2; a.c1 = c1; a.c2 = c2; a.eps = eps; a.grad_mul = grad_mul;
-    a.step = step; a.key = key;
+    AdamArgs a;
+    const int rc = fill_adam_args(a, "nvfp4_adamw_step", p, master, grad, grad_kind, grad_cols, grad_stride, sa, sb, extra, grad_mul, m, v,
+                                  ms, vs, tail, unit, n, vbits, mbits, state_block, lr, decay, b1, b2, c1, c2, eps, step, key, ctrl,
+                                  scale_out, scratch);
+    if (rc != NVFP4_OK) return rc;
     const unsigned grid = static_cast<unsigned>((n + 4095) / 4096);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     bool ok = false;
@@ -514,6 +581,65 @@ extern "C" int nvfp4_adamw_step(void* p, int master, const void* grad, int grad_
     }
     NVFP4_REQUIRE(ok, NVFP4_ERR_UNSUPPORTED, "nvfp4_adamw_step: no kernel for moments m%d v%d", mbits, vbits);
     return launch_status("nvfp4_adamw_step");
+}
+
+// ---- update + next weight packings in one cooperative launch -------------------------------------------------------
+namespace nvfp4 {
+template <int MASTER, int VB, bool M4, bool NL, int B>
+static int launch_prepack(AdamArgs& a, PackArgs& k, cudaStream_t st) {
+    auto kernel = adamw_prepack_kernel<MASTER, VB, M4, NL, B>;
+    static int resident = 0;   // CTAs that fit the GPU at once (per instantiation; the library serves one GPU model)
+    if (!resident) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1 || sms < 1) {
+            set_error("nvfp4_adamw_step_prepack: cannot size the cooperative grid");
+            return NVFP4_ERR_LAUNCH;
+        }
+        resident = per_sm * sms;
+    }
+    const int64_t chunks = (a.n + 4095) / 4096;
+    const int64_t tiles = (round128(k.rows) / 128) * (round128(k.cols) / 128);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(std::max(chunks, tiles), resident));
+    void* args[] = {&a, &k};
+    const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(256), args, 0, st);
+    if (e != cudaSuccess) {
+        set_error("nvfp4_adamw_step_prepack: cooperative launch failed: %s", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return launch_status("nvfp4_adamw_step_prepack");
+}
+}  // namespace nvfp4
+
+extern "C" int nvfp4_adamw_step_prepack(void* p, int master, const void* grad, int grad_kind, int64_t grad_cols, int64_t grad_stride,
+                                        const float* sa, const float* sb, const float* extra, float grad_mul, void* m, void* v,
+                                        float* ms, float* vs, int8_t* tail, int64_t rows, int64_t cols, int vbits, int mbits,
+                                        int nonlinear_m, int state_block, float lr, float decay, float b1, float b2, float c1,
+                                        float c2, float eps, uint32_t step, uint32_t key, const float* ctrl, float* scale_out,
+                                        uint8_t* packed, uint8_t* scales, uint8_t* packed_t, uint8_t* scales_t, void* scratch,
+                                        int* status, nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(rows > 0 && cols > 0 && scale_out && packed && scales && packed_t && scales_t && scratch, NVFP4_ERR_ARG,
+                  "nvfp4_adamw_step_prepack: null pointer or empty weight");
+    for (const void* q : {static_cast<const void*>(packed), static_cast<const void*>(scales), static_cast<const void*>(packed_t),
+                          static_cast<const void*>(scales_t)})
+        NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_adamw_step_prepack: outputs must be 16-byte aligned");
+    AdamArgs a;
+    const int rc = fill_adam_args(a, "nvfp4_adamw_step_prepack", p, master, grad, grad_kind, grad_cols, grad_stride, sa, sb, extra, grad_mul,
+                                  m, v, ms, vs, tail, nullptr, rows * cols, vbits, mbits, state_block, lr, decay, b1, b2, c1, c2, eps,
+                                  step, key, ctrl, scale_out, scratch);
+    if (rc != NVFP4_OK) return rc;
+    PackArgs k{packed, scales, packed_t, scales_t, rows, cols,
+               reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + SCRATCH_ADAM_OFFSET + 16), status};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const bool m8v8 = mbits == 8 && vbits == 8;
+    if (master == 17 && m8v8 && state_block == 512) return launch_prepack<17, 8, false, false, 512>(a, k, st);
+    if (master == 17 && m8v8 && state_block == 128) return launch_prepack<17, 8, false, false, 128>(a, k, st);
+    if (master == 24 && m8v8 && state_block == 512) return launch_prepack<24, 8, false, false, 512>(a, k, st);
+    if (master == 32 && mbits == 8 && vbits == 16 && state_block == 512) return launch_prepack<32, 16, false, false, 512>(a, k, st);
+    if (master == 17 && mbits == 4 && vbits == 4 && nonlinear_m) return launch_prepack<17, 4, true, true, 512>(a, k, st);
+    set_error("nvfp4_adamw_step_prepack: no kernel for master %d with moments m%d v%d and state block %d", master, mbits, vbits, state_block);
+    return NVFP4_ERR_UNSUPPORTED;
 }
 
 extern "C" int nvfp4_adamw_plain(float* p, const float* grad, float* m, float* v, int64_t n, float grad_mul, float lr, float decay,

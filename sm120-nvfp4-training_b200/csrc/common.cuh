@@ -27,6 +27,7 @@ int launch_status(const char* what);
 //   [0, 4112)     amax partials + ticket          (quantize.cu)
 //   [4112, 4128)  the four amax results of nvfp4_quantize
 //   [4128, 4144)  AdamW: amax bits, ticket        (adamw.cu)
+//   [4144, 4148)  AdamW with weight packings: arrival counter of the grid barrier
 constexpr int SCRATCH_AMAX_OUT_OFFSET = 4112;
 constexpr int SCRATCH_ADAM_OFFSET = 4128;
 constexpr int SCRATCH_BYTES = 4160;

@@ -55,8 +55,12 @@ def configure(model, mode, fmt, *, lr=1e-4, tiles=4, warps=4, prepack=False, pac
         raise ValueError('Unknown compute mode or storage format')
     if tiles not in (1, 2, 4, 8, 16) or warps not in (4, 8, 16) or mma_warps not in (4, 8):
         raise ValueError('Unsupported optimizer launch configuration')
-    if prepack or compact_embedding:
-        raise NotImplementedError('optimizer-emitted packings and compact tied embeddings are not enabled in this interface')
+    if compact_embedding:
+        raise NotImplementedError('compact tied embeddings are not enabled in this interface')
+    if prepack and remat:
+        raise ValueError('Choose one weight encoding strategy')
+    if prepack and FORMATS[fmt][0] == 8:
+        raise ValueError('Prepacking is not enabled for FP8 storage')
     if mode == 'bf16':
         raise NotImplementedError("precision='bf16' is the dense control path of the reference; it is not part of the NVFP4 hot path")
     master = FORMATS[fmt][0]
@@ -105,6 +109,8 @@ def configure(model, mode, fmt, *, lr=1e-4, tiles=4, warps=4, prepack=False, pac
         if not isinstance(layer, nn.Linear):
             continue
         p = layer.weight
+        if counts[id(p)] == 1 and p.numel() >= 4096 and not remat:
+            p._v6_packable = True        # the optimizer may emit this weight's packings (captured steps with prepack)
         if master != 32 and counts[id(p)] == 1 and p.numel() >= 4096:
             if master == 8:
                 if not direct:

@@ -99,7 +99,15 @@ class _LinearFn(torch.autograd.Function):
         src = w.detach() if (fp8 and pts is not None) else _source(w)
         if pts is None and (paired or remat):
             pts = weight_scale(src)
-        if paired:
+        emitted = getattr(w, "_v6_pack", None) if contiguous and not remat and pts is not None else None
+        if emitted is not None and emitted["version"] == w._version and emitted["scale"] is pts:
+            # the optimizer wrote both packings of this weight, against this scale, in its last update
+            data, scale, td, ts = emitted["buffers"]
+            b = Packed(data, scale, pts, w.dtype)
+            _STATS["quant"] += 2
+            _STATS["reused_weight_amax"] += 1
+            _STATS["prepacked_weight"] = _STATS.get("prepacked_weight", 0) + 1
+        elif paired:
             data, scale, pts, td, ts = encode(w, pts) if fp8 else pair(src, pts)
             b = Packed(data, scale, pts, w.dtype)
             _STATS["quant"] += 2

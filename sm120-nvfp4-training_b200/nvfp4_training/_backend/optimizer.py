@@ -352,6 +352,22 @@ class AdamW6(AdamW):
         store = p.view(torch.uint8) if p.dtype == torch.float8_e4m3fn else p
         if not scaled and grad.dtype not in (torch.float32, torch.bfloat16):
             grad = grad.float()   # FP16 leaf gradients of FP16 masters: exact widening
+        nonlinear = g['format'].endswith('_sqrt')
+        emit = getattr(p, '_v6_pack', None)
+        if emit is not None and cache and p.ndim == 2 and (master, vb, mb, nonlinear, g['state_block']) in nat.PREPACK_FORMATS:
+            # one launch: the update, the next tensor scale and both packings of the updated weight
+            nat.adamw_step_prepack(store, master, grad, s['m'], s.get('v'), s['ms'], s['vs'], pack=emit['buffers'], vbits=vb, mbits=mb,
+                                   nonlinear_m=nonlinear, state_block=g['state_block'], hyper=self._hyper(g, t), step=t,
+                                   key=self.keys[p], grad_kind=2 if scaled else None, grad_cols=p.shape[-1] if scaled else 1,
+                                   grad_stride=grad.shape[-1] if scaled else 1, sa=sa, sb=sb,
+                                   extra=p.grad if (pack is not None and p.grad is not None) else None, grad_mul=self._grad_mul(),
+                                   tail=s.get('tail'), ctrl=ctrl, scale_out=scale)
+            torch.autograd.graph.increment_version(p)
+            emit['version'] = p._version
+            s['step'] = t
+            self._publish_scale(p, scale)
+            self.prepacked = getattr(self, 'prepacked', 0) + 1
+            return
         nat.adamw_step(store, master, grad, s['m'], s.get('v'), s['ms'], s['vs'], vbits=vb, mbits=mb,
                        nonlinear_m=g['format'].endswith('_sqrt'), state_block=g['state_block'], hyper=self._hyper(g, t), step=t,
                        key=self.keys[p], grad_kind=2 if scaled else None, grad_cols=p.shape[-1] if scaled else 1,

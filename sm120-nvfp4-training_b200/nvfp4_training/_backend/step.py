@@ -65,6 +65,16 @@ class StaticStep:
                         self.scales[p] = rng.weight_scale(src).clone()
                 else:
                     self.scales[p] = cached[3]
+        # packings the optimizer will keep current: filled once from the present weights, then rewritten by every update
+        self.packs = []
+        if self.group.get('prepack', False) and self.group['cache_scale']:
+            with torch.no_grad():
+                for p in owners:
+                    if getattr(p, '_v6_packable', False) and p in self.scales and p.ndim == 2 and p.is_contiguous() \
+                            and p.dtype != torch.float8_e4m3fn:
+                        d, s, _, dt, st = rng.pair(p.detach(), self.scales[p])
+                        p._v6_pack = dict(buffers=(d, s, dt, st), version=p._version, scale=self.scales[p])
+                        self.packs.append(p)
         optimizer.zero_grad(set_to_none=True)
         self.graph = torch.cuda.CUDAGraph()
         # captured kernel nodes inherit the stream's priority: the main line of the step is placed before the overlapped
@@ -165,6 +175,9 @@ class StaticStep:
                     p._v4_scale = (p._version, p.data_ptr(), self.stream.cuda_stream, self.scales[p])
                 elif hasattr(p, '_v4_scale'):
                     del p._v4_scale
+            for p in self.packs:
+                if hasattr(p, '_v6_pack'):
+                    del p._v6_pack
             if self.sr_calls and rng._SEED == self.seed_end:
                 rng._SEED = (self.seed0 + self.index * self.sr_calls) & 0xffffffff
             del self.opt._graph_owner

@@ -37,6 +37,8 @@ _SIGNATURES = {
     "nvfp4_dequantize": (I32, [P, P, P, I64, I64, I64, I32, I32, P, I64, P]),
     "nvfp4_adamw_step": (I32, [P, I32, P, I32, I64, I64, P, P, P, F, P, P, P, P, P, P, I64, I32, I32, I32, I32,
                                  F, F, F, F, F, F, F, U32, U32, P, P, P, P]),
+    "nvfp4_adamw_step_prepack": (I32, [P, I32, P, I32, I64, I64, P, P, P, F, P, P, P, P, P, I64, I64, I32, I32, I32, I32,
+                                         F, F, F, F, F, F, F, U32, U32, P, P, P, P, P, P, P, P, P]),
     "nvfp4_adamw_plain": (I32, [P, P, P, P, I64, F, F, F, F, F, F, F, F, P, P]),
     "nvfp4_split_init": (I32, [P, I64, I32, P, P, P]),
     "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I64, I32, P, P]),
@@ -255,6 +257,26 @@ def adamw_step(p, master, grad, m, v, ms, vs, *, vbits, mbits, nonlinear_m, stat
                                      hyper["decay"], hyper["b1"], hyper["b2"], hyper["c1"], hyper["c2"], hyper["eps"],
                                      int(step) & 0xFFFFFFFF, int(key) & 0xFFFFFFFF, ptr(ctrl), ptr(scale_out),
                                      scratch(dev).data_ptr(), stream_of(p)))
+
+
+PREPACK_FORMATS = {(17, 8, 8, False, 512), (17, 8, 8, False, 128), (24, 8, 8, False, 512), (32, 16, 8, False, 512), (17, 4, 4, True, 512)}
+
+
+def adamw_step_prepack(p, master, grad, m, v, ms, vs, *, pack, vbits, mbits, nonlinear_m, state_block, hyper, step, key, grad_kind=None,
+                       grad_cols=1, grad_stride=1, sa=None, sb=None, extra=None, grad_mul=1.0, tail=None, ctrl=None, scale_out=None):
+    """nvfp4_adamw_step on a 2-D weight plus the next forward's packings pack = (d, s, dt, st), written by the same launch."""
+    if grad_kind is None:
+        grad_kind = 0 if grad.dtype == torch.float32 else 1
+    dev = p.device
+    d, s, dt, st = pack
+    with torch.cuda.device(dev):
+        check(lib().nvfp4_adamw_step_prepack(p.data_ptr(), master, grad.data_ptr(), grad_kind, grad_cols, grad_stride, ptr(sa), ptr(sb),
+                                             ptr(extra), float(grad_mul), m.data_ptr(), ptr(v), ms.data_ptr(), vs.data_ptr(), ptr(tail),
+                                             p.shape[0], p.shape[1], vbits, mbits, int(bool(nonlinear_m)), state_block, hyper["lr"],
+                                             hyper["decay"], hyper["b1"], hyper["b2"], hyper["c1"], hyper["c2"], hyper["eps"],
+                                             int(step) & 0xFFFFFFFF, int(key) & 0xFFFFFFFF, ptr(ctrl), scale_out.data_ptr(),
+                                             d.data_ptr(), s.data_ptr(), dt.data_ptr(), st.data_ptr(), scratch(dev).data_ptr(),
+                                             status_word(dev).data_ptr(), stream_of(p)))
 
 
 def adamw_plain(p, grad, m, v, *, hyper, grad_mul=1.0, ctrl=None):

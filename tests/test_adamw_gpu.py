@@ -169,3 +169,40 @@ def test_scale_reduction_is_independent_of_earlier_amax_calls(native):
     native.adamw_step(p, 17, grad, m, v, ms, vs, vbits=8, mbits=8, nonlinear_m=False, state_block=512, hyper=h, step=2, key=9,
                       scale_out=scale)
     assert scale.item() == native.amax(p.view(1, -1))[1].item()
+
+
+@pytest.mark.parametrize("fmt", ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "half16_m4v4_sqrt"])
+@pytest.mark.parametrize("rows,cols", [(256, 512), (130, 200), (1024, 3072)])
+def test_update_with_emitted_packings_equals_update_then_quantise(native, fmt, rows, cols):
+    """nvfp4_adamw_step_prepack: same master / moments / scale as nvfp4_adamw_step, and packings byte-identical to the pair
+    quantiser run on the updated weight with the new scale (two updates in a row: the grid barrier word resets itself)."""
+    from _util import signs_dev
+    master, vb, mb = O.FORMATS[fmt]
+    n = rows * cols
+    g = torch.Generator().manual_seed(rows + cols)
+    w = (torch.randn(rows, cols, generator=g) * 0.02).cuda()
+    states = []
+    for _ in range(2):
+        if master == 32:
+            p, tail = w.clone(), None
+        else:
+            p, tail = native.split_init(w, master)
+        states.append((p, tail, *_state(n, fmt)))
+    (pa, ta, ma, va, msa, vsa), (pb, tb, mb_, vb_, msb, vsb) = states
+    sa_, sb_ = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    mp, kp = native.round128(rows), native.round128(cols)
+    pack = (torch.zeros((mp, kp // 2), dtype=torch.uint8, device="cuda"), torch.zeros((mp // 128 * 32, kp // 64 * 16), dtype=torch.uint8, device="cuda"),
+            torch.zeros((kp, mp // 2), dtype=torch.uint8, device="cuda"), torch.zeros((kp // 128 * 32, mp // 64 * 16), dtype=torch.uint8, device="cuda"))
+    for t in (1, 2):
+        grad = (torch.randn(rows, cols, generator=g) * 3e-3).bfloat16().cuda()
+        h = O.adam_hyper(3e-4, (0.9, 0.95), 1e-8, 0.1, t)
+        common = dict(vbits=vb, mbits=mb, nonlinear_m=fmt.endswith("_sqrt"), state_block=O.state_block(fmt), hyper=h, step=t, key=4242)
+        native.adamw_step(pa.view(-1), master, grad.view(-1), ma, va, msa, vsa, tail=None if ta is None else ta.view(-1), scale_out=sa_, **common)
+        native.adamw_step_prepack(pb, master, grad, mb_, vb_, msb, vsb, pack=pack, tail=tb, scale_out=sb_, **common)
+        native.check_status()
+        for got, want in ((pb, pa), (mb_, ma), (vb_, va), (msb, msa), (vsb, vsa), (tb, ta), (sb_, sa_)):
+            if want is not None:
+                assert torch.equal(got.view(torch.uint8).flatten(), want.view(torch.uint8).flatten())
+        d, s, _, dt, st = native.quantize(pa, signs_dev(), mp, kp, 0, False, 0, given_scale=sa_.reshape(()), pair=True)
+        for got, want, name in zip(pack, (d, s, dt, st), ("payload", "scales", "payload^T", "scales^T")):
+            assert torch.equal(got, want), f"{fmt} {rows}x{cols} step {t}: {name}"

@@ -172,3 +172,40 @@ def test_layers_sharing_an_input_reuse_its_packing_and_edits_invalidate_it():
     assert torch.equal(back[1].data, fresh[1].data) and torch.equal(back[0].scale, fresh[0].scale)
     a, b = quant.dual(x, signs, sr=True), quant.dual(x, signs, sr=True)
     assert a[0].data is not b[0].data and not torch.equal(a[0].data, b[0].data)
+
+
+@pytest.mark.parametrize("profile", ["balanced", "short128", "conservative", "same_as_v5", "experimental_m4v4"])
+def test_optimizer_emitted_packings_leave_captured_training_unchanged(profile):
+    """prepack: the update kernel also writes the next forward's weight packings (one cooperative launch per weight).  The
+    packings are byte-identical to what the forward would compute, so weights and optimizer state after captured steps are
+    the same with and without it, and the forward of the captured step holds no weight quantiser any more."""
+    import nvfp4_training as nv
+    from nvfp4_training._runtime import load_runtime
+    rng = load_runtime()[2]
+    x, y = batch(256, seed=3)
+    results = []
+    for prepack in (False, True):
+        rng.reset_stats(5)
+        model = nv.enable_nvfp4(make_model(seed=4).cuda(), profile=profile, lr=1e-3)
+        opt = model.nvfp4_optimizer
+        opt.param_groups[0]["prepack"] = prepack
+        nv.train_step(model, mse, x, y)
+        with nv.capture_step(model, mse, x, y, steps=4) as graph:
+            seen = rng.stats()
+            losses = [graph.step(x, y).item() for _ in range(4)]
+        nv.check_finite(model)
+        assert not any(hasattr(p, "_v6_pack") for p in model.parameters())      # the capture took its buffers with it
+        if prepack:
+            assert seen.get("prepacked_weight", 0) == 3 and getattr(opt, "prepacked", 0) == 3
+        nv.train_step(model, mse, x, y)      # eager training continues on the ordinary path
+        results.append((losses, state_bytes(model)))
+    assert results[0][0] == results[1][0]
+    assert same(results[0][1], results[1][1])
+
+
+def test_prepack_is_refused_where_the_reference_refuses_it():
+    from nvfp4_training._backend.engine import configure
+    with pytest.raises(ValueError, match="one weight encoding strategy"):
+        configure(make_model(), "fp4", "half16_v8", prepack=True, remat=True, direct=True)
+    with pytest.raises(ValueError, match="FP8 storage"):
+        configure(make_model(), "fp4", "float8_m4v4_sqrt", prepack=True, direct=True)
