@@ -141,14 +141,14 @@ def c1_input(seed: int) -> torch.Tensor:
 # workload: quantise + dequantise of 4096 x 4096 BF16 (RNE pass and Philox-SR pass, both with H16 RHT)
 # ------------------------------------------------------------------------------------------------
 def run_quant(args, rank, world, device):
-    import oracle as O
     from nvfp4_training import _native as nat
+    from nvfp4_training._backend.quant import get_signs
 
     nbuf = 8  # 8 x 32 MiB of input = 256 MiB, twice the L2
     base = c1_input(rank)
     host = [base.roll(i, 0).contiguous().pin_memory() for i in range(nbuf)]
     dev = [h.to(device) for h in host]
-    signs = torch.from_numpy(O.default_signs(0)).to(device)
+    signs = get_signs(device, seed=0)     # this benchmark configuration names sign seed 0; the package default is 1
     out_bf16 = torch.empty((4096, 4096), dtype=torch.bfloat16, device=device)
     launches = 0
 
@@ -216,7 +216,7 @@ def run_quant(args, rank, world, device):
                    "rows_sharded_across_gpus": world},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                      "traffic": NCU_TRAFFIC["quant_c1"], "traffic_source": NCU_TRAFFIC_SOURCE["quant_c1"],
-                     "kernel": "quant_tile_kernel<bf16,row> (RNE+RHT, scale given)", "kernel_ms": kernel_ms,
+                     "kernel": "quant_stream_kernel<bf16,row,RNE,RHT> (scale given)", "timing": "30 launches on rotated inputs captured as one CUDA graph, CUDA events around the replay", "kernel_ms": kernel_ms,
                      "peak_source": pk["source"]},
         "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "kernels_us": {"amax": amax_ms * 1e3, "quantize_rne_rht": kernel_ms * 1e3, "quantize_philox_sr_rht": sr_ms * 1e3,
@@ -348,13 +348,9 @@ def quant_microbench(device, reps=30):
 C3 = dict(layers=32, dim=3072, heads=24, ffn=8192, vocab=32000, seq=2048, micro_batch=4)
 
 
-def run_train(args, rank, world, device):
+def build_c3(cfg, world, device):
     import nvfp4_training as nv
-    from nvfp4_training import _native as nat
-    from nvfp4_training._workloads.llama import Decoder, linear_parameters, token_loss, warm_attention
-    cfg = dict(C3)
-    if args.layers:
-        cfg["layers"] = args.layers
+    from nvfp4_training._workloads.llama import Decoder
     torch.manual_seed(0)
     with torch.device(device):
         model = Decoder(layers=cfg["layers"], dim=cfg["dim"], heads=cfg["heads"], ffn=cfg["ffn"], vocab=cfg["vocab"], seq=cfg["seq"])
@@ -362,66 +358,134 @@ def run_train(args, rank, world, device):
     model.nvfp4_optimizer.param_groups[0]["prepack"] = os.environ.get("NVFP4_PREPACK", "0") == "1"
     if world > 1:
         nv.enable_data_parallel(model)
-    n_linear = linear_parameters(model)
-    n_params = sum(p.numel() for p in model.parameters())
-    mb, seq = cfg["micro_batch"], cfg["seq"]
-    tokens = mb * seq
-    total = args.warmup + args.steps + 6
-    gen = torch.Generator().manual_seed(0)
-    ids = torch.randint(0, cfg["vocab"], (total, world, mb, seq + 1), generator=gen)[:, rank].contiguous().pin_memory()
+    return model
+
+
+def time_c3(model, cfg, ids, steps, warmup, world, device, profiler_range=False, e2e=True):
+    """Capture the whole step once, replay it: (ms per step device-timed, ms per step with host inputs, losses, calls, clocks)."""
+    import nvfp4_training as nv
+    from nvfp4_training._workloads.llama import token_loss
     x0, y0 = ids[0, :, :-1].to(device), ids[0, :, 1:].to(device)
-    warm_attention(model, mb, seq, device)
-    torch.cuda.reset_peak_memory_stats()
+    total = warmup + 2 * steps + 2
     graph = nv.capture_step(model, token_loss, x0, y0, steps=total)
-    captured_calls = graph.library_calls   # library calls recorded into the step's graph (>= one kernel each)
+    calls = graph.library_calls
     dev_ids = ids.to(device)
-    losses = []
+    losses, e2e_ms = [], None
     with graph:
-        step_i = 0
-        for _ in range(args.warmup):
-            graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
+        i = 0
+        for _ in range(warmup):
+            graph.step(dev_ids[i, :, :-1], dev_ids[i, :, 1:]); i += 1
         barrier(world)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(args.profiler_range):
+        with ClockSampler(torch.cuda.current_device()) as clk, ProfilerRange(profiler_range):
             ev0.record()
-            for _ in range(args.steps):
-                loss = graph.step(dev_ids[step_i, :, :-1], dev_ids[step_i, :, 1:]); step_i += 1
+            for _ in range(steps):
+                loss = graph.step(dev_ids[i, :, :-1], dev_ids[i, :, 1:]); i += 1
             ev1.record()
             barrier(world)
-        ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps, world, device)
+        ms = max_over_ranks(ev0.elapsed_time(ev1) / steps, world, device)
         losses.append(float(loss.item()))
-        # end to end: token ids come from pinned host memory, the loss goes back to the host, every step
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        xb, yb = torch.empty_like(x0), torch.empty_like(y0)
-        barrier(world)
-        e0.record()
-        for _ in range(3):
-            xb.copy_(ids[step_i, :, :-1], non_blocking=True); yb.copy_(ids[step_i, :, 1:], non_blocking=True)
-            losses.append(float(graph.step(xb, yb).item())); step_i += 1
-        e1.record()
-        barrier(world)
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / 3, world, device)
-        launches = graph.sr_calls  # SR quantiser launches per step; the full count is derived below
+        if e2e:
+            # end to end: token ids come from pinned host memory, the loss goes back to the host, every step
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            xb, yb = torch.empty_like(x0), torch.empty_like(y0)
+            barrier(world)
+            e0.record()
+            for _ in range(steps):
+                xb.copy_(ids[i, :, :-1], non_blocking=True); yb.copy_(ids[i, :, 1:], non_blocking=True)
+                losses.append(float(graph.step(xb, yb).item())); i += 1
+            e1.record()
+            barrier(world)
+            e2e_ms = max_over_ranks(e0.elapsed_time(e1) / steps, world, device)
+    return ms, e2e_ms, losses, calls, clk.summary()
+
+
+def incumbent_gemm_tflops(device, tokens, d_in, d_out, reps=20):
+    """The library's NVFP4 GEMM (torch._scaled_mm -> cuBLASLt) on the same packed operands, for comparison only; None when
+    this torch build does not accept them."""
+    try:
+        from nvfp4_training._backend import quant
+        f4, f8 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+        x = torch.randn((tokens, d_in), device=device).bfloat16()
+        w = (torch.randn((d_out, d_in), device=device) * 0.02).bfloat16()
+        a, b = quant.quantize(x), quant.quantize(w)
+        run = lambda i: torch._scaled_mm(a.data.view(f4), b.data.view(f4).t(), a.scale.view(f8), b.scale.view(f8), out_dtype=torch.bfloat16)
+        ms = time_kernel(run, reps)
+        return 2.0 * tokens * d_in * d_out / (ms * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def run_train(args, rank, world, device):
+    import nvfp4_training as nv
+    from nvfp4_training import _native as nat
+    from nvfp4_training._workloads.llama import linear_parameters, warm_attention
+    os.environ.setdefault("NVFP4_SR_RNG", "philox")
+    sr_rng = os.environ["NVFP4_SR_RNG"].lower()
+    cfg = dict(C3)
+    if args.layers:
+        cfg["layers"] = args.layers
+    mb, seq = cfg["micro_batch"], cfg["seq"]
+    tokens = mb * seq
+    total = args.warmup + 2 * args.steps + 2
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab"], (total, world, mb, seq + 1), generator=gen)[:, rank].contiguous().pin_memory()
+    model = build_c3(cfg, world, device)
+    n_linear = linear_parameters(model)
+    n_params = sum(p.numel() for p in model.parameters())
+    warm_attention(model, mb, seq, device)
+    torch.cuda.reset_peak_memory_stats()
+    ms, e2e_ms, losses, captured_calls, clocks = time_c3(model, cfg, ids, args.steps, args.warmup, world, device, args.profiler_range)
     nv.check_finite(model)
     peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
-    n_layers_linear = sum(1 for m in model.modules() if isinstance(m, torch.nn.Linear))
-    # counted, not derived: every call into the C-ABI library made while the step was captured launches at least one
-    # kernel of this repository (amax, quantisers, GEMMs, AdamW, RoPE, SwiGLU) and is replayed once per step
-    kernel_launches = captured_calls
+    comm = None
+    if world > 1:
+        # the same captured step with the collectives left out (timing only): what the gradient exchange costs the step
+        red = model.nvfp4_optimizer.reducer
+        per_step = dict(collectives=red.collectives, bytes=sum(p.numel() * (2 if red.has_slot(p) else 4) for p in model.parameters()))
+        red.elide = True
+        quiet_ms = time_c3(model, cfg, ids, max(3, args.steps // 2), 3, world, device, e2e=False)[0]
+        red.elide = False
+        comm = {"ms_per_step_with_collectives": ms, "ms_per_step_collectives_elided": quiet_ms, "exposed_ms": ms - quiet_ms,
+                "collectives_per_step": per_step["collectives"], "bytes_reduced_per_step": per_step["bytes"],
+                "note": "elided = the same graph captured without the all-reduces; results of that run are discarded"}
+    variants = {}
+    if world == 1 and not args.no_variants:
+        # the same step with the reference's integer-hash stochastic rounding (bit-exact to the reference's generator)
+        del model
+        torch.cuda.empty_cache()
+        other = "hash" if sr_rng == "philox" else "philox"
+        os.environ["NVFP4_SR_RNG"] = other
+        alt = build_c3(cfg, world, device)
+        alt_ms = time_c3(alt, cfg, ids, max(3, args.steps // 2), 3, world, device, e2e=False)[0]
+        os.environ["NVFP4_SR_RNG"] = sr_rng
+        variants[f"sr_rng_{other}"] = {"ms_per_step": alt_ms, "tokens_per_s": tokens / (alt_ms * 1e-3)}
+        del alt
+        torch.cuda.empty_cache()
     pk = peaks()
     gemm_ms, gemm_tf = gemm_microbench(device, tokens, cfg["dim"], cfg["ffn"])
     c2_ms, c2_tf = gemm_microbench(device, C2["tokens"], C2["d_in"], C2["d_out"])
     q_ms, q_gbs = quant_microbench(device)
     fp4_peak = 4.0 * pk["bf16_tflops"]
     linear_flops = 6.0 * n_linear * tokens
+    # lower bound of the step from its three kinds of work: FP4 GEMMs at the tensor peak, BF16 attention at the sustained
+    # BF16 peak, optimizer and quantiser traffic at the HBM peak
+    attn_flops = 3.5 * cfg["layers"] * 4.0 * mb * seq * seq * cfg["dim"] / 2
+    adam_bytes = 10.0 * n_params
+    quant_bytes = 3.125 * (2 * n_linear + tokens * cfg["layers"] * 2 * (cfg["dim"] * 3 + cfg["ffn"]) + tokens * cfg["layers"] * (4 * cfg["dim"] + 2 * cfg["ffn"]))
+    bound_ms = (linear_flops / (fp4_peak * 1e12) + attn_flops / ((pk["bf16_sustained"] or pk["bf16_tflops"]) * 1e12)
+                + (adam_bytes + quant_bytes) / (pk["hbm_gbs"] * 1e9)) * 1e3
     line = {
         "metric": "nvfp4_train_tokens_per_s", "value": world * tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate); bf16 attention", "data": "synthetic",
         "config": {"workload": f"C3: Llama-style decoder {n_params / 1e9:.2f}B params ({cfg['layers']} layers, d {cfg['dim']}, {cfg['heads']} heads, "
-                               f"SwiGLU {cfg['ffn']}, vocab {cfg['vocab']}), seq {seq}, micro-batch {mb} per GPU, balanced profile, "
-                               "compressed AdamW lr 3e-4 betas (0.9,0.95) wd 0.1, whole step replayed as one CUDA graph",
+                               f"SwiGLU {cfg['ffn']}, vocab {cfg['vocab']}; q/k/v and gate/up as fused projections), seq {seq}, micro-batch {mb} "
+                               "per GPU, balanced profile, compressed AdamW lr 3e-4 betas (0.9,0.95) wd 0.1, whole step replayed as one CUDA graph",
                    "global_batch": world * mb, "seq_len": seq, "parallelism": f"dp{world}",
+                   "sr_rng": {"philox": "philox4x32-10 bits into the hardware stochastic conversion (cvt.rs.e2m1x4)",
+                              "hash": "the reference's 32-bit integer hash, 24-bit uniforms"}[sr_rng],
+                   "prepack": os.environ.get("NVFP4_PREPACK", "0") == "1",
                    "l2": "per-step working set (weights 7.6 GB + activations) exceeds the 126 MB L2"},
         "tokens_per_s_per_gpu": tokens / (ms * 1e-3), "train_peak_GiB": peak_gib, "loss": losses[0],
         "linear_tflops_in_step": linear_flops / (ms * 1e-3) / 1e12,
@@ -430,29 +494,37 @@ def run_train(args, rank, world, device):
                      / (C2["tokens"] * C2["d_in"] + C2["d_in"] * C2["d_out"] + C2["tokens"] * C2["d_out"]),
                      "traffic_source": NCU_TRAFFIC_SOURCE["gemm_c2"] + ", per launch, scaled to this layer by the sum of the three matrices' sizes",
                      "kernel": f"gemm_kernel<256, paired CTAs> fprop+dgrad+wgrad of a {cfg['dim']}x{cfg['ffn']} layer at {tokens} tokens",
-                     "kernel_ms": gemm_ms, "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)", "frac_of_nominal_9PF": gemm_tf / FP4_NOMINAL_TFLOPS},
+                     "kernel_ms": gemm_ms, "timing": "CUDA events around 20 eager launches of the triple on rotated operand sets, after the timed "
+                     "training region (87 us per launch, far above the host's launch interval)",
+                     "peak_source": pk["source"] + " bf16 GEMM x4 (FP4 issue rate)", "frac_of_nominal_9PF": gemm_tf / FP4_NOMINAL_TFLOPS,
+                     "step_bound_ms": bound_ms, "step_frac": bound_ms / ms},
         "kernels": {"c2_linear_gemm_tflops": c2_tf, "c2_ms": c2_ms, "c1_quantize_GBps": q_gbs, "c1_quantize_ms": q_ms,
-                    "c1_frac_of_hbm": q_gbs / pk["hbm_gbs"]},
-        "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(xb.numel() + yb.numel()) * 8,
-                "d2h_bytes_per_step": 4},
-        "gpu_launches": kernel_launches * args.steps,
-        "clocks": clk.summary(),
+                    "c1_frac_of_hbm": q_gbs / pk["hbm_gbs"],
+                    "incumbent_c2_fprop_tflops": incumbent_gemm_tflops(device, C2["tokens"], C2["d_in"], C2["d_out"])},
+        "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(2 * mb * seq) * 8,
+                "d2h_bytes_per_step": 4, "steps": args.steps},
+        "gpu_launches": captured_calls * args.steps,
+        "clocks": clocks,
     }
+    if variants:
+        line["variants"] = variants
+    if comm:
+        line["comm"] = comm
     if rank == 0 and world == 1 and not args.skip_cpu:
-        line["cpu_baseline"] = cpu_train_baseline(cfg, budget_tokens=512)
+        line["cpu_baseline"] = cpu_train_baseline(cfg)
     return line
 
 
-def cpu_train_baseline(cfg, budget_tokens=512):
-    """The oracle on the host cores: the seven linears of ONE decoder layer (quantise, three FP32 matmuls on the decoded
-    operands, rescale) at `budget_tokens` tokens plus the compressed AdamW of that layer; extrapolated to the full token
-    count and layer count.  Attention, norms, embedding and head are not included: an optimistic CPU figure."""
+CPU_BUDGET_TOKENS = 256   # tokens of the bounded CPU sample, the same in the GPU arm's cpu_baseline and in --impl reference
+
+
+def cpu_layer_seconds(cfg, budget_tokens):
+    """One decoder layer on the oracle: its four NVFP4 linears (fused q/k/v, o, fused gate/up, down) forward + input
+    gradient + weight gradient at `budget_tokens` tokens, and the compressed AdamW of those weights."""
     import oracle as O
-    torch.set_num_threads(os.cpu_count() or 1)
     d, f = cfg["dim"], cfg["ffn"]
-    shapes = [(d, d)] * 4 + [(d, f)] * 2 + [(f, d)]
+    shapes = [(d, 3 * d), (d, d), (d, 2 * f), (f, d)]
     g = torch.Generator().manual_seed(0)
-    tokens_full = cfg["micro_batch"] * cfg["seq"]
     t_lin = t_adam = 0.0
     signs = O.default_signs()
     for k, n in shapes:
@@ -463,9 +535,9 @@ def cpu_train_baseline(cfg, budget_tokens=512):
         t0 = time.perf_counter()
         row, col = O.dual(xb, signs=signs)
         wr, wc = O.weight_pair(wb, kind="f16")
-        y = O.matmul_packed(row, wr, budget_tokens, n)
+        O.matmul_packed(row, wr, budget_tokens, n)
         grow, gcol = O.dual(gb, sr_mode=O.SR_HASH, signs=signs, seed=7)
-        dx = O.matmul_packed(grow, wc, budget_tokens, k)
+        O.matmul_packed(grow, wc, budget_tokens, k)
         raw = O.matmul_packed(gcol, col, n, k, out_bf16=True)
         t_lin += time.perf_counter() - t0
         m = np.zeros(n * k, np.int8); v = np.zeros(n * k, np.uint8)
@@ -474,12 +546,21 @@ def cpu_train_baseline(cfg, budget_tokens=512):
         t0 = time.perf_counter()
         O.adam_update("half16_v8", wb.reshape(-1).copy(), grad, m, v, ms, vs, step=1, key=1, hyper=O.adam_hyper(3e-4, (0.9, 0.95), 1e-8, 0.1, 1), grad_kind=1)
         t_adam += time.perf_counter() - t0
-    layer_s = t_lin * (tokens_full / budget_tokens) + t_adam
-    step_s = layer_s * cfg["layers"]
+    return t_lin, t_adam
+
+
+def cpu_train_baseline(cfg, budget_tokens=CPU_BUDGET_TOKENS, samples=3):
+    """The oracle on the host cores, median of `samples` runs of one layer, extrapolated to the full token count and layer
+    count.  Attention, norms, embedding and head are not included: an optimistic CPU figure."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    tokens_full = cfg["micro_batch"] * cfg["seq"]
+    runs = sorted(cpu_layer_seconds(cfg, budget_tokens) for _ in range(samples))
+    t_lin, t_adam = runs[len(runs) // 2]
+    step_s = (t_lin * (tokens_full / budget_tokens) + t_adam) * cfg["layers"]
     return {"value": tokens_full / step_s, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
-            "sample": f"one decoder layer's 7 linears fwd+dgrad+wgrad at {budget_tokens} tokens ({t_lin:.1f} s) + its compressed AdamW "
-                      f"({t_adam:.1f} s) on the CPU oracle; extrapolated x{tokens_full // budget_tokens} tokens x{cfg['layers']} layers; "
-                      "attention / embedding / head excluded"}
+            "sample": f"median of {samples}: one decoder layer's 4 fused linears fwd+dgrad+wgrad at {budget_tokens} tokens ({t_lin:.1f} s) + its "
+                      f"compressed AdamW ({t_adam:.1f} s) on the CPU oracle; extrapolated x{tokens_full // budget_tokens} tokens "
+                      f"x{cfg['layers']} layers; attention / embedding / head excluded"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -636,9 +717,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return None
     cfg = dict(C3)
-    res = None
-    for _ in range(max(1, min(args.steps, 3))):
-        res = cpu_train_baseline(cfg, budget_tokens=256)
+    res = cpu_train_baseline(cfg)
     tokens = cfg["micro_batch"] * cfg["seq"]
     return {"impl": "reference", "metric": "nvfp4_train_tokens_per_s", "value": res["value"], "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": tokens / res["value"] * 1e3, "higher_is_better": True,
@@ -660,6 +739,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the decoder depth (smoke runs only; the metric needs the default)")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-variants", action="store_true", help="train workload: skip the second run with the other SR generator")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = dist_env()

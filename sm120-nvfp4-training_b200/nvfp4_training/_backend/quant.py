@@ -70,13 +70,13 @@ def round128(n: int) -> int:
     return (n + 127) // 128 * 128
 
 
-def get_signs(device) -> torch.Tensor:
-    """16 random +-1 floats from a CPU generator seeded with 1 (nvfp4_fast_v2.py:145-150)."""
-    device = torch.device(device)
-    if device not in _SIGNS:
-        gen = torch.Generator(device="cpu").manual_seed(1)
-        _SIGNS[device] = (torch.randint(0, 2, (16,), generator=gen).float() * 2 - 1).to(device)
-    return _SIGNS[device]
+def get_signs(device, seed: int = 1) -> torch.Tensor:
+    """16 random +-1 floats from a CPU generator; the reference seeds it with 1 (nvfp4_fast_v2.py:145-150)."""
+    key = (torch.device(device), int(seed))
+    if key not in _SIGNS:
+        gen = torch.Generator(device="cpu").manual_seed(int(seed))
+        _SIGNS[key] = (torch.randint(0, 2, (16,), generator=gen).float() * 2 - 1).to(key[0])
+    return _SIGNS[key]
 
 
 @dataclass

@@ -41,6 +41,7 @@ class GradientReducer:
         self._bucket = []         # (param, group, gradient) of small dense gradients waiting for a shared collective
         self._bucket_fill = 0
         self.collectives = 0      # collectives started since begin()
+        self.elide = False        # timing experiments only: record no collective at all (results are then wrong on purpose)
 
     # ---- used by the linear layer's backward ------------------------------------------------------------
     def has_slot(self, p) -> bool:
@@ -101,22 +102,25 @@ class GradientReducer:
             if self._bucket_fill >= self.bucket_bytes:
                 self._flush_bucket()
             return self._pop(self.depth, wait)
-        work = dist.all_reduce(tensor, group=self.group, async_op=True)
-        self.collectives += 1
+        work = self._all_reduce(tensor)
         if extra is not None:
-            work = _Both(work, dist.all_reduce(extra, group=self.group, async_op=True))
-            self.collectives += 1
+            work = _Both(work, self._all_reduce(extra))
         self.launched.append(p)
         self._queue.append(([(p, group, pack)], work))
         return self._pop(self.depth, wait)
+
+    def _all_reduce(self, tensor):
+        self.collectives += 1
+        if self.elide:
+            return _Done()
+        return dist.all_reduce(tensor, group=self.group, async_op=True)
 
     def _flush_bucket(self):
         """One FP32 buffer, one collective; the members' gradients become views of the reduced buffer."""
         if not self._bucket:
             return
         flat = torch.cat([t.reshape(-1).float() for _, _, t in self._bucket])
-        work = dist.all_reduce(flat, group=self.group, async_op=True)
-        self.collectives += 1
+        work = self._all_reduce(flat)
         items, at = [], 0
         for p, group, t in self._bucket:
             items.append((p, group, (flat[at:at + t.numel()].view(t.shape), None, None)))
@@ -139,6 +143,11 @@ class GradientReducer:
             else:
                 ready.extend((q, g, k, w) for q, g, k in items)
         return ready
+
+
+class _Done:
+    def wait(self):
+        pass
 
 
 class _Both:
