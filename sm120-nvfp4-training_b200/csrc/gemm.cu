@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace nvfp4 {
 
@@ -638,7 +639,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     }
     static int sm_count[64] = {};
     if (dev < 64 && !sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    const int sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
+    // NVFP4_GEMM_RESERVE_SMS=n keeps n SMs out of the persistent grid, for kernels that run beside the GEMMs and cannot share
+    // an SM with a CTA that holds all of its shared memory (the collectives of data-parallel training)
+    static const int reserve = [] { const char* e = getenv("NVFP4_GEMM_RESERVE_SMS"); return e ? std::max(0, atoi(e)) : 0; }();
+    const int sms = std::max(2, (dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148) - reserve);
     g.tiles_n = g.N / BN;
     g.tiles_m = g.M / (BM * Cfg::CTAS);
     if constexpr (PAIR) {

@@ -1,27 +1,48 @@
 """One LoRA update (forward, loss, backward, optional clipping, fused AdamW) captured as a CUDA graph.
 
-Follows the reference's LoRAStep (src/precision_lora/graph.py:15-111): warm-up and capture run real updates, after
-which parameters, optimizer state, stochastic-rounding counters, other buffers and both RNG states are put back, so
-capturing never counts as training.  The SR seed of every NVFP4 base is a device counter incremented inside the graph.
+Interface and guarantees of the reference's LoRAStep (src/precision_lora/graph.py:15-111): constructor arguments, `step`,
+`close`, context-manager use and error messages are the same, and capturing never counts as training.  Warm-up and
+recording run real updates; `_Rewind` remembers everything such an update touches (adapter weights, optimizer state, the
+stochastic-rounding counters of the NVFP4 bases, other module buffers, both RNG states) and puts it back afterwards.  The
+SR seed of every NVFP4 base is a device counter incremented inside the graph, so replays draw fresh noise.
 """
 from __future__ import annotations
-
-from functools import lru_cache
 
 import torch
 
 from .core import _FrozenFP4, lora_parameters
 from .packed import PackedNVFP4Linear
 
+_STREAMS = {}
 
-@lru_cache(maxsize=None)
+
 def _capture_stream(device):
-    # one side stream per device for every capture: library workspaces are keyed by stream and would pile up otherwise
-    return torch.cuda.Stream(device=device)
+    """One side stream per device for every capture: library workspaces are keyed by stream and would pile up otherwise."""
+    key = torch.device(device)
+    if key not in _STREAMS:
+        _STREAMS[key] = torch.cuda.Stream(device=key)
+    return _STREAMS[key]
 
 
-def _snapshot(tensors):
-    return [t.detach().clone() for t in tensors]
+class _Rewind:
+    """Values of everything a LoRA update changes, taken at construction; restore() writes them back in place."""
+
+    def __init__(self, optimizer, params, tensors):
+        self.optimizer = optimizer
+        self.tensors = [(t, t.detach().clone()) for t in (*params, *tensors)]
+        self.state = {p: {k: (v.clone() if torch.is_tensor(v) else v) for k, v in optimizer.state.get(p, {}).items()} for p in params}
+        self.cuda_rng, self.cpu_rng = torch.cuda.get_rng_state(), torch.get_rng_state()
+
+    @torch.no_grad()
+    def restore(self):
+        for live, value in self.tensors:
+            live.copy_(value)
+        for p, before in self.state.items():
+            for key, value in self.optimizer.state[p].items():
+                if torch.is_tensor(value):      # state created by the warm-up of a fresh optimizer goes back to zero
+                    value.copy_(before[key]) if key in before else value.zero_()
+        torch.cuda.set_rng_state(self.cuda_rng)
+        torch.set_rng_state(self.cpu_rng)
 
 
 class LoRAStep:
@@ -34,73 +55,54 @@ class LoRAStep:
         if not params or any(not p.is_cuda or p.device != params[0].device for p in params):
             raise ValueError("CUDA LoRA model required")
         device = params[0].device
-        if not isinstance(optimizer, torch.optim.AdamW) or any(not g.get("fused") for g in optimizer.param_groups):
+        groups = optimizer.param_groups if isinstance(optimizer, torch.optim.AdamW) else None
+        if groups is None or not all(g.get("fused") for g in groups):
             raise ValueError("LoRA capture requires fused torch.optim.AdamW")
-        if {id(p) for p in params} != {id(p) for g in optimizer.param_groups for p in g["params"]}:
+        if {id(p) for p in params} != {id(p) for g in groups for p in g["params"]}:
             raise ValueError("Optimizer must contain exactly the LoRA parameters")
         if any(not torch.is_tensor(t) or t.device != device for t in samples):
             raise ValueError("Pass fixed-shape CUDA tensor inputs")
         self.model, self.optimizer, self.params = model, optimizer, params
-        self.capture_flags = [g.get("capturable", False) for g in optimizer.param_groups]
-        for group in optimizer.param_groups:
-            group["capturable"] = True
+        self.loss_fn, self.max_grad_norm = loss_fn, max_grad_norm
         self.inputs = [t.detach().clone() for t in samples]
-        self.closed = False
-        self.original_training = model.training
+        self.closed, self.original_training = False, model.training
+        self.capture_flags = [g.get("capturable", False) for g in groups]
+        for g in groups:
+            g["capturable"] = True          # the fused optimizer then keeps its step counters on the device
         bases = [m for m in model.modules() if isinstance(m, _FrozenFP4)]
         self.seed_buffers = [m.sr_seed for m in bases]
-        frozen_ids = {id(b) for m in bases for b in m.buffers()}
-        self.other_buffers = [b for b in model.buffers() if id(b) not in frozen_ids]
-        kept = dict(params=_snapshot(params), seeds=_snapshot(self.seed_buffers), buffers=_snapshot(self.other_buffers),
-                    cuda_rng=torch.cuda.get_rng_state(), cpu_rng=torch.get_rng_state(),
-                    state={p: {k: v.clone() if torch.is_tensor(v) else v for k, v in optimizer.state.get(p, {}).items()}
-                           for p in params})   # a started optimizer is preserved too
-
-        def update():
-            optimizer.zero_grad(set_to_none=False)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = loss_fn(model, *self.inputs)
-            loss.backward()
-            if max_grad_norm is not None:
-                torch.nn.utils.clip_grad_norm_(params, max_grad_norm)
-            optimizer.step()
-            self.loss = loss.detach()
-
-        @torch.no_grad()
-        def rewind():
-            for group, values in ((params, kept["params"]), (self.seed_buffers, kept["seeds"]),
-                                  (self.other_buffers, kept["buffers"])):
-                for t, value in zip(group, values):
-                    t.copy_(value)
-            for p, before in kept["state"].items():
-                for key, value in optimizer.state[p].items():
-                    if torch.is_tensor(value):
-                        if key in before:
-                            value.copy_(before[key])
-                        else:
-                            value.zero_()
-            torch.cuda.set_rng_state(kept["cuda_rng"])
-            torch.set_rng_state(kept["cpu_rng"])
-
-        side = _capture_stream(device)
-        side.wait_stream(torch.cuda.current_stream())
+        owned_by_bases = {id(b) for m in bases for b in m.buffers()}
+        self.other_buffers = [b for b in model.buffers() if id(b) not in owned_by_bases]
+        rewind = _Rewind(optimizer, params, (*self.seed_buffers, *self.other_buffers))
+        side, main = _capture_stream(device), torch.cuda.current_stream()
+        side.wait_stream(main)
         try:
             with torch.cuda.stream(side):
                 for _ in range(warmup):
-                    update()
-            torch.cuda.current_stream().wait_stream(side)
+                    self._update()
+            main.wait_stream(side)
             torch.cuda.synchronize()
-            rewind()
+            rewind.restore()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=side):
-                update()
-            rewind()
+                self._update()
+            rewind.restore()
             optimizer.zero_grad(set_to_none=False)
         except BaseException:
             torch.cuda.synchronize()
-            rewind()
+            rewind.restore()
             self._restore_flags()
             raise
+
+    def _update(self):
+        self.optimizer.zero_grad(set_to_none=False)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = self.loss_fn(self.model, *self.inputs)
+        loss.backward()
+        if self.max_grad_norm is not None:
+            torch.nn.utils.clip_grad_norm_(self.params, self.max_grad_norm)
+        self.optimizer.step()
+        self.loss = loss.detach()
 
     def _restore_flags(self):
         for group, flag in zip(self.optimizer.param_groups, self.capture_flags):
@@ -111,11 +113,12 @@ class LoRAStep:
             raise RuntimeError("LoRA graph is closed")
         if self.model.training != self.original_training:
             raise RuntimeError("Do not change train/eval mode during graph replay")
-        if len(batch) != len(self.inputs) or any(
-                a.shape != b.shape or a.dtype != b.dtype or a.device != b.device for a, b in zip(batch, self.inputs)):
+        matches = len(batch) == len(self.inputs) and all(
+            given.shape == held.shape and given.dtype == held.dtype and given.device == held.device for given, held in zip(batch, self.inputs))
+        if not matches:
             raise ValueError("Graph inputs must match the captured shape, dtype and device")
-        for dst, src in zip(self.inputs, batch):
-            dst.copy_(src)
+        for held, given in zip(self.inputs, batch):
+            held.copy_(given)
         self.graph.replay()
         return self.loss.detach()
 

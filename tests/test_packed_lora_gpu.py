@@ -133,7 +133,7 @@ def test_rope_matches_oracle():
 def source(n, k, seed=91):
     """A checkpoint with only the minimum scale-block padding (multiples of 16 columns), not 128-alignment."""
     from precision_lora import _packed_cuda as cuda
-    from precision_lora.packed import _indices
+    from precision_lora.packed import _scale_positions as _indices
     g = torch.Generator(device="cuda").manual_seed(seed)
     full = F.pad(torch.randn(n, k, generator=g, device="cuda", dtype=torch.bfloat16) * .08, (0, -k % 128, 0, -n % 128))
     q, s, p = cuda.quantize(full)
