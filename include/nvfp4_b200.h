@@ -120,6 +120,10 @@ int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, int64_t rows,
  * scales and pts.  given_scale != null reuses a tensor scale (then pts_out may be null); pair != 0
  * additionally writes the transposed packing (contiguous FP32/FP16/BF16 weights, RNE, no RHT).
  * sr: 0 RNE, NVFP4_Q_SR_HASH or NVFP4_Q_SR_PHILOX.  scratch: nvfp4_amax_scratch_bytes() bytes.
+ * Without a given scale the call is two launches (amax, then the quantiser), except for a BF16 source with unit column
+ * stride and 16-byte aligned rows of at most 7 x 128 x 128 elements per SM (4096 x 4096 on 148 SMs): that one is loaded
+ * into shared memory once and amax, scale and packing come from ONE cooperative launch (same bytes; `status` reports a
+ * grid-barrier wait that ran out; the environment variable NVFP4_QUANT_RESIDENT=0 keeps the two launches).
  */
 int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp,
                    int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,

@@ -28,8 +28,10 @@ int launch_status(const char* what);
 //   [4112, 4128)  the four amax results of nvfp4_quantize
 //   [4128, 4144)  AdamW: amax bits, ticket        (adamw.cu)
 //   [4144, 4148)  AdamW with weight packings: arrival counter of the grid barrier
+//   [4148, 4156)  resident quantiser: magnitude maximum, arrival counter of its grid barrier
 constexpr int SCRATCH_AMAX_OUT_OFFSET = 4112;
 constexpr int SCRATCH_ADAM_OFFSET = 4128;
+constexpr int SCRATCH_RESIDENT_OFFSET = 4148;
 constexpr int SCRATCH_BYTES = 4160;
 
 __host__ __device__ __forceinline__ int64_t round128(int64_t n) { return (n + 127) / 128 * 128; }

@@ -7,6 +7,8 @@
 //                        Serves 2-byte sources with unit column stride and 16-byte aligned rows.
 //   quant_tile_kernel    one 128 x 128 tile per CTA with per-thread loads: every other source (FP32, E4M3 x unit,
 //                        arbitrary strides, unaligned bases).
+//   quant_resident_kernel  amax + row packing in one cooperative launch for BF16 tensors that fit the GPU's shared
+//                        memory (one read of the source from HBM); used by the nvfp4_quantize operator.
 #include "quant_core.cuh"
 #include "async.cuh"
 
@@ -629,6 +631,235 @@ static int try_stream(const void* x, int dtype, int64_t rows, int64_t cols, int6
 }
 
 // ================================================================================================
+// resident quantiser: tensor amax AND row packing in one launch, the source read from HBM once
+// ================================================================================================
+// A BF16 tensor of at most QR_MAX_TILES x (number of SMs) source tiles (33.9 MB on 148 SMs) fits the GPU's shared memory.
+// One CTA per SM loads its tiles with TMA (all loads in flight at once), takes the magnitude maximum of what arrived,
+// meets the other CTAs at a grid barrier (cooperative launch, bounded wait), derives the tensor scale from the global
+// maximum with the amax kernel's expression, and encodes its tiles from shared memory.  A warp overwrites the 4 KB source
+// slab it has just read into registers with the slab's 1 KB of payload, which leaves by a TMA store.
+constexpr int QR_MAX_TILES = 7;
+constexpr int QR_WARPS = 16;
+constexpr int QR_THREADS = QR_WARPS * 32;
+
+struct __align__(128) ResidentSmem {
+    uint16_t in[QR_MAX_TILES][TILE * TILE];
+    uint64_t full[QR_MAX_TILES];
+    uint32_t warp_best[QR_WARPS];
+    uint32_t amax_bits;
+    int proceed;
+    int abort;
+};
+
+struct ResidentArgs {
+    const float* signs;
+    const int32_t* seed_base;
+    unsigned int* amax_word;   // zero between launches: maximum of the magnitude bits over all CTAs
+    unsigned int* arrivals;    // zero between launches: grid barrier
+    float* out4;               // the four results of the amax kernel
+    int* status;
+    Orient R;
+    int tiles_r, tiles_c;
+};
+
+template <int SR, bool R_RHT, bool FAST>
+__device__ __forceinline__ void resident_encode(ResidentSmem& S, const CUtensorMap* map_row, const ResidentArgs& a,
+                                                const float (&sg)[16], float inv, int my_tiles, int warp, int lane) {
+    using namespace aop;
+    const uint32_t seed = a.R.seed + (a.seed_base ? static_cast<uint32_t>(__ldg(a.seed_base)) : 0u);
+    const int64_t gpr = a.R.kp >> 4;
+    for (int item = warp; item < my_tiles * 8; item += QR_WARPS) {
+        const int k = item >> 3, slab = (item & 7) * QS_SLAB;
+        const int t = blockIdx.x + k * gridDim.x;
+        const int rt = t / a.tiles_c, ct = t - rt * a.tiles_c;
+        uint16_t* rows16 = S.in[k] + slab * TILE;       // this warp's 16 source rows of 256 bytes
+        uint4 raw[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4* src = reinterpret_cast<const uint4*>(rows16 + (4 * i + (lane >> 3)) * TILE + (lane & 7) * 16);
+            raw[i][0] = src[0]; raw[i][1] = src[1];
+        }
+        __syncwarp();                                   // the whole slab is in registers: its memory becomes the staging area
+        uint8_t* out = reinterpret_cast<uint8_t*>(rows16);
+        uint8_t* out_sc = out + QS_SLAB * 64;
+        const uint64_t group0 = static_cast<uint64_t>(rt * TILE + slab) * gpr + ct * 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int lr = 4 * i + (lane >> 3), gc = lane & 7;
+            float v[16];
+            unpack16<NVFP4_BF16>(raw[i][0], raw[i][1], v);
+            if constexpr (R_RHT) hadamard16_unscaled(v, sg);
+            const uint64_t group = group0 + static_cast<uint32_t>(lr * static_cast<int>(gpr) + gc);
+            uint32_t sb;
+            const uint2 p = encode16<SR, FAST>(v, R_RHT, inv, seed, static_cast<uint32_t>(group) << 4, group, sb);
+            *reinterpret_cast<uint2*>(out + lr * 64 + gc * 8) = p;
+            out_sc[lr * 8 + gc] = static_cast<uint8_t>(sb);
+        }
+        fence_async_shared();
+        __syncwarp();
+        {
+            const int piece_row = slab + (lane >> 1), piece_half = lane & 1;
+            const uint32_t piece = *reinterpret_cast<const uint32_t*>(out_sc + (lane >> 1) * 8 + piece_half * 4);
+            *reinterpret_cast<uint32_t*>(a.R.scales + (static_cast<int64_t>(rt) * (a.R.kp >> 6) + ct * 2) * 512 + piece_half * 512 +
+                                         (piece_row & 31) * 16 + (piece_row >> 5) * 4) = piece;
+        }
+        if (lane == 0) {
+            tma_store_2d(map_row, ct * 64, rt * TILE + slab, out);
+            bulk_commit();
+        }
+    }
+    if (lane == 0) bulk_wait_all();
+}
+
+template <int SR, bool R_RHT>
+__global__ void __launch_bounds__(QR_THREADS, 1)
+quant_resident_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_row, const ResidentArgs a) {
+    using namespace aop;
+    extern __shared__ __align__(128) uint8_t resident_smem_raw[];
+    ResidentSmem& S = *reinterpret_cast<ResidentSmem*>(resident_smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = a.tiles_r * a.tiles_c;
+    const int my_tiles = (n_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    if (tid == 0) {
+        for (int k = 0; k < my_tiles; ++k) mbar_init(&S.full[k], 1);
+        S.abort = 0;
+        fence_barrier_init();
+        for (int k = 0; k < my_tiles; ++k) {
+            const int t = blockIdx.x + k * gridDim.x;
+            const int rt = t / a.tiles_c, ct = t - rt * a.tiles_c;
+            mbar_expect_tx(&S.full[k], QS_TILE_BYTES);
+            tma_load_2d(S.in[k], &map_in, ct * TILE, rt * TILE, &S.full[k]);
+        }
+    }
+    __syncthreads();
+    // ---- phase 1: magnitude maximum of this CTA's tiles (|bf16| orders like its 15 magnitude bits) ----
+    uint32_t best2 = 0;
+    bool landed = true;
+    for (int k = 0; k < my_tiles && landed; ++k) {
+        landed = __all_sync(0xffffffffu, mbar_wait(&S.full[k], 0, &S.abort));
+        if (!landed) break;
+        const uint4* p = reinterpret_cast<const uint4*>(S.in[k]) + warp * 128 + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 q = p[32 * j];
+            best2 = __vmaxu2(best2, q.x & 0x7fff7fffu); best2 = __vmaxu2(best2, q.y & 0x7fff7fffu);
+            best2 = __vmaxu2(best2, q.z & 0x7fff7fffu); best2 = __vmaxu2(best2, q.w & 0x7fff7fffu);
+        }
+    }
+    uint32_t best = max(best2 & 0xffffu, best2 >> 16);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, d));
+    if (lane == 0) S.warp_best[warp] = best;
+    __syncthreads();
+    // ---- grid barrier: the global maximum is complete after it ----
+    if (tid == 0) {
+        uint32_t b = 0;
+        for (int w = 0; w < QR_WARPS; ++w) b = max(b, S.warp_best[w]);
+        atomicMax(a.amax_word, b);
+        __threadfence();
+        atomicAdd(a.arrivals, 1u);
+        const long long t0 = clock64();
+        int ok = S.abort ? 0 : 1;
+        while (ok && *reinterpret_cast<volatile unsigned int*>(a.arrivals) < gridDim.x) {
+            __nanosleep(100);
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) ok = 0;
+        }
+        __threadfence();
+        S.amax_bits = *reinterpret_cast<volatile unsigned int*>(a.amax_word);
+        S.proceed = ok;
+        if (!ok && a.status) *a.status = NVFP4_ERR_TIMEOUT;
+    }
+    __syncthreads();
+    if (S.proceed) {
+        const float amax = __uint_as_float(S.amax_bits << 16);
+        const float floor_a = fmaxf(amax, 1.e-12f), c = 1.f / (6.f * 448.f);
+        const float plain = __fmul_rn(__fmul_rn(1.f, floor_a), c), rotated = __fmul_rn(__fmul_rn(4.f, floor_a), c);
+        const float pts = R_RHT ? rotated : plain;
+        if (tid == 0 && blockIdx.x == 0) {
+            a.out4[0] = amax; a.out4[1] = plain; a.out4[2] = rotated; a.out4[3] = __fdiv_rn(floor_a, 2688.f);
+            *a.R.pts = pts;
+        }
+        float sg[16];
+#pragma unroll
+        for (int l = 0; l < 16; ++l) sg[l] = a.signs ? __ldg(a.signs + l) : 1.f;
+        const ScaleMath sm = scale_math(pts);
+        if (sm.fast) resident_encode<SR, R_RHT, true>(S, &map_row, a, sg, sm.inv, my_tiles, warp, lane);
+        else resident_encode<SR, R_RHT, false>(S, &map_row, a, sg, sm.inv, my_tiles, warp, lane);
+    }
+    // the last CTA to leave zeroes both words for the next launch
+    __syncthreads();
+    if (tid == 0 && atomicAdd(a.arrivals, 1u) == 2u * gridDim.x - 1u) { *a.amax_word = 0u; __threadfence(); *a.arrivals = 0u; }
+}
+
+template <int SR, bool R_RHT>
+static cudaError_t launch_resident_one(const CUtensorMap& mi, const CUtensorMap& mr, const ResidentArgs& a, int grid, cudaStream_t st) {
+    const size_t smem = sizeof(ResidentSmem);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(quant_resident_kernel<SR, R_RHT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    void* args[] = {const_cast<CUtensorMap*>(&mi), const_cast<CUtensorMap*>(&mr), const_cast<ResidentArgs*>(&a)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(quant_resident_kernel<SR, R_RHT>), dim3(grid), dim3(QR_THREADS),
+                                       args, smem, st);
+}
+
+static bool resident_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("NVFP4_QUANT_RESIDENT");
+        on = !(e && e[0] == '0');
+    }
+    return on != 0;
+}
+
+// amax + row packing of a BF16 tensor that fits shared memory.  NVFP4_ERR_UNSUPPORTED: the caller runs the two launches.
+static int try_resident(const void* x, int dtype, int64_t rows, int64_t cols, int64_t rs, int64_t cs, const float* signs,
+                        const int32_t* base, int flags, uint32_t seed, uint8_t* packed, uint8_t* scales, float* pts_out,
+                        void* scratch, int* status, cudaStream_t st) {
+    if (!resident_enabled() || !stream_enabled() || dtype != NVFP4_BF16 || cs != 1 || (flags & NVFP4_Q_HI_FIRST)) return NVFP4_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (rs * 2) % 16 != 0 || rs < cols) return NVFP4_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(scratch)) & 15) != 0)
+        return NVFP4_ERR_UNSUPPORTED;
+    static int sms = 0, coop = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int64_t rp = round128(rows), cp = round128(cols), tiles = rp / 128 * (cp / 128);
+    if (!coop || tiles > static_cast<int64_t>(QR_MAX_TILES) * sms) return NVFP4_ERR_UNSUPPORTED;
+    CUtensorMap mi, mr;
+    if (!aop::make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, static_cast<uint64_t>(cols), static_cast<uint64_t>(rows),
+                          static_cast<uint64_t>(rs) * 2, TILE, TILE))
+        return NVFP4_ERR_UNSUPPORTED;
+    if (!aop::make_map_2d(&mr, CU_TENSOR_MAP_DATA_TYPE_UINT8, packed, static_cast<uint64_t>(cp / 2), static_cast<uint64_t>(rp),
+                          static_cast<uint64_t>(cp / 2), 64, QS_SLAB))
+        return NVFP4_ERR_UNSUPPORTED;
+    char* sc = static_cast<char*>(scratch);
+    ResidentArgs a{signs, base, reinterpret_cast<unsigned int*>(sc + SCRATCH_RESIDENT_OFFSET),
+                   reinterpret_cast<unsigned int*>(sc + SCRATCH_RESIDENT_OFFSET + 4),
+                   reinterpret_cast<float*>(sc + SCRATCH_AMAX_OUT_OFFSET), status,
+                   Orient{packed, scales, pts_out, cp, seed, flags}, static_cast<int>(rp / 128), static_cast<int>(cp / 128)};
+    const int grid = static_cast<int>(std::min<int64_t>(tiles, sms));
+    const bool rht = flags & NVFP4_Q_RHT;
+    const int sr = sr_of_flags(flags);
+    cudaError_t e;
+    if (sr == SR_NONE) e = rht ? launch_resident_one<SR_NONE, true>(mi, mr, a, grid, st) : launch_resident_one<SR_NONE, false>(mi, mr, a, grid, st);
+    else if (sr == SR_HASH) e = rht ? launch_resident_one<SR_HASH, true>(mi, mr, a, grid, st) : launch_resident_one<SR_HASH, false>(mi, mr, a, grid, st);
+    else e = rht ? launch_resident_one<SR_PHILOX, true>(mi, mr, a, grid, st) : launch_resident_one<SR_PHILOX, false>(mi, mr, a, grid, st);
+    if (e != cudaSuccess) {
+        set_error("nvfp4_quantize: cooperative launch of the resident quantiser failed: %s", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return launch_status("nvfp4_quantize");
+}
+
+// ================================================================================================
 // dequantiser: one thread per 16-element group
 // ================================================================================================
 template <bool OUT_BF16>
@@ -790,10 +1021,10 @@ extern "C" int nvfp4_quantize_fp8_weight(const uint8_t* w, const float* unit, in
                               const_cast<float*>(pts), 0, 0, col_packed, col_scales, const_cast<float*>(pts), 0, 0, nullptr, stream);
 }
 
-extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp,
-                              int64_t kp, int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,
-                              const int32_t* seed_base, int pair, uint8_t* packed, uint8_t* scales, float* pts_out,
-                              uint8_t* packed_t, uint8_t* scales_t, void* scratch, int* status, nvfp4_stream_t stream) {
+static int quantize_op(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp, int64_t kp, int sr,
+                       int rht, uint32_t seed, const float* signs, const float* given_scale, const int32_t* seed_base, int pair,
+                       uint8_t* packed, uint8_t* scales, float* pts_out, uint8_t* packed_t, uint8_t* scales_t, void* scratch,
+                       int* status, bool one_launch, nvfp4_stream_t stream) {
     NVFP4_REQUIRE(x && packed && scales && signs, NVFP4_ERR_ARG, "nvfp4_quantize: null pointer");
     NVFP4_REQUIRE(m > 0 && k > 0 && s0 >= 0 && s1 >= 0, NVFP4_ERR_ARG, "nvfp4_quantize: empty/broadcast/negative strides unsupported");
     NVFP4_REQUIRE(mp == round128(m) && kp == round128(k), NVFP4_ERR_ARG,
@@ -801,6 +1032,12 @@ extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, in
     NVFP4_REQUIRE(sr == 0 || sr == NVFP4_Q_SR_HASH || sr == NVFP4_Q_SR_PHILOX, NVFP4_ERR_ARG, "nvfp4_quantize: bad sr mode %d", sr);
     NVFP4_REQUIRE(given_scale || (pts_out && scratch), NVFP4_ERR_ARG, "nvfp4_quantize: need pts_out and scratch when no scale is given");
     const float* pts = given_scale;
+    if (!given_scale && !pair && s1 == 1 && one_launch) {
+        // a tensor that fits shared memory: maximum, scale and packing from one read of the source
+        const int rc = try_resident(x, dtype, m, k, s0, s1, signs, seed_base, (rht ? NVFP4_Q_RHT : 0) | sr, seed, packed, scales, pts_out,
+                                    scratch, status, reinterpret_cast<cudaStream_t>(stream));
+        if (rc != NVFP4_ERR_UNSUPPORTED) return rc;
+    }
     if (!given_scale) {
         // the four amax results land in the scratch tail; the scale this call needs also goes to pts_out
         float* out4 = reinterpret_cast<float*>(static_cast<char*>(scratch) + SCRATCH_AMAX_OUT_OFFSET);
@@ -822,6 +1059,14 @@ extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, in
     }
     return nvfp4_quantize_tile(x, dtype, m, k, s0, s1, signs, seed_base, packed, scales, pts, flags, seed, nullptr, nullptr, nullptr,
                                0, 0, status, stream);
+}
+
+extern "C" int nvfp4_quantize(const void* x, int dtype, int64_t m, int64_t k, int64_t s0, int64_t s1, int64_t mp,
+                              int64_t kp, int sr, int rht, uint32_t seed, const float* signs, const float* given_scale,
+                              const int32_t* seed_base, int pair, uint8_t* packed, uint8_t* scales, float* pts_out,
+                              uint8_t* packed_t, uint8_t* scales_t, void* scratch, int* status, nvfp4_stream_t stream) {
+    return quantize_op(x, dtype, m, k, s0, s1, mp, kp, sr, rht, seed, signs, given_scale, seed_base, pair, packed, scales, pts_out,
+                       packed_t, scales_t, scratch, status, true, stream);
 }
 
 extern "C" int nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* pts, int64_t kp, int64_t rows,
@@ -878,6 +1123,6 @@ extern "C" int nvfp4_quantize_static(const void* x, int dtype, int64_t m, int64_
     e = cudaMemsetAsync(static_cast<char*>(scratch) + offsetof(AmaxScratch, ticket), 0, sizeof(unsigned int),
                         reinterpret_cast<cudaStream_t>(stream));
     NVFP4_REQUIRE(e == cudaSuccess, NVFP4_ERR_LAUNCH, "nvfp4_quantize_static: cannot clear the ticket: %s", cudaGetErrorString(e));
-    return nvfp4_quantize(x, dtype, m, k, s0, s1, mp, kp, sr, rht, seed, signs, nullptr, seed_base, 0, packed, scales, pts_out,
-                          nullptr, nullptr, scratch, nullptr, stream);
+    return quantize_op(x, dtype, m, k, s0, s1, mp, kp, sr, rht, seed, signs, nullptr, seed_base, 0, packed, scales, pts_out,
+                       nullptr, nullptr, scratch, nullptr, false, stream);
 }

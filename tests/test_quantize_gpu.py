@@ -198,3 +198,38 @@ def test_weight_pair_matches_reference_cuda_kernel(native, golden_cuda_quant):
     _cmp(d, s, (g["pair_data"], g["pair_scale"]))
     _cmp(dt, st, (g["pair_data_t"], g["pair_scale_t"]))
     assert np.float32(native.amax(w)[1].item()) == g["pair_pts"][0]
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("rht", [False, True])
+def test_one_launch_operator_equals_amax_then_quantise(native, mode, rht):
+    """BF16 tensors that fit shared memory take amax, scale and packing in one cooperative launch; the result is the
+    two-launch result (amax kernel, then the quantiser with that scale) byte for byte, on repeated calls (the barrier
+    words return to zero), under graph replay, and next to a tensor just above the size limit that takes two launches."""
+    flag, _ = MODES[mode]
+    signs = signs_dev()
+    for shape in ((4096, 4096), (1024, 640), (300, 1000), (4224, 4096)):
+        x = outlier_tensor(shape, seed=shape[0] + shape[1]).cuda()
+        mp, kp = native.round128(shape[0]), native.round128(shape[1])
+        four = native.amax(x).clone()
+        scale = four[2 if rht else 1].clone()
+        want = native.quantize(x, signs, mp, kp, flag, rht, 11, given_scale=scale)
+        for _ in range(3):
+            got = native.quantize(x, signs, mp, kp, flag, rht, 11)
+            assert torch.equal(got[2], scale)
+            assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    x = outlier_tensor((2048, 2048), seed=3).cuda()
+    want = native.quantize(x, signs, 2048, 2048, flag, rht, 5)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        native.quantize(x, signs, 2048, 2048, flag, rht, 5)      # scratch of this stream exists before the capture
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        got = native.quantize(x, signs, 2048, 2048, flag, rht, 5)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
