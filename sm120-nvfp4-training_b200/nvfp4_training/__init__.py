@@ -42,11 +42,13 @@ def capture_frozen(model, compute, *inputs, backward=True, warmup=2):
     return capture(model, compute, *inputs, backward=backward, warmup=warmup)
 
 
-def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2):
+def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2, peer_timeout=None):
     """Data-parallel replicas: NCCL all-reduce of the gradients, overlapped with backward.  Weight gradients of converted
-    layers are reduced in place, one collective each; small dense gradients share FP32 buckets of bucket_mb megabytes."""
+    layers are reduced in place, one collective each; small dense gradients share FP32 buckets of bucket_mb megabytes.
+    Ranks must agree on the converted layers (checked here, on the host); peer_timeout (seconds) adds a host-side liveness
+    check before every eager step.  nvfp4_training.distributed.verify_replicas compares a digest of all state."""
     from .distributed import enable_data_parallel as enable
-    return enable(model, process_group, bucket_mb=bucket_mb, depth=depth)
+    return enable(model, process_group, bucket_mb=bucket_mb, depth=depth, peer_timeout=peer_timeout)
 
 
 def prepare_training(model, *, profile="balanced", precision="fp4", remat=False, lr=1e-4, betas=(0.9, 0.999), eps=1e-8,

@@ -12,10 +12,20 @@ The reference is single-GPU; this module is new.  Design:
     identical on all ranks because weights, rounding keys and step numbers are.
 Works eagerly and under CUDA-graph capture (the update of a parameter is deferred by `depth` parameters so that its
 collective has time to finish).  Plain loads / NCCL only: no peer-memory kernels, no TMA multicast.
+
+Failures are detected on the host, between steps, never by a kernel that waits for a peer:
+  * `verify_layout` (run by enable_data_parallel): every rank must hold the same slots, bucket size and depth, or all ranks
+    raise before the first collective could pair buffers of different sizes;
+  * `replica_digest` / `verify_replicas`: a SHA-256 over parameters, buffers and optimizer state; ranks that drifted apart
+    (or loaded different checkpoints) raise on every rank, naming the ranks that disagree with rank 0;
+  * `PeerWatch`: a gloo control group with a short timeout; `check()` before a step raises on the surviving ranks, naming
+    the ranks that did not answer, instead of letting the next NCCL collective wait for a process that has left.
 """
 from __future__ import annotations
 
+import hashlib
 from collections import deque
+from datetime import timedelta
 
 import torch
 import torch.distributed as dist
@@ -59,6 +69,9 @@ class GradientReducer:
 
     # ---- eager protocol (backward_step / step) ----------------------------------------------------------
     def begin(self, params, capturing=False):
+        watch = getattr(self, "watch", None)
+        if watch is not None and not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()):
+            watch.check()
         self._streaming = bool(capturing)
         self._works.clear()
         self._queue.clear()
@@ -145,6 +158,75 @@ class GradientReducer:
         return ready
 
 
+    def layout(self):
+        """What has to agree across ranks for the collectives to pair up: slot sizes in order, bucket size, depth."""
+        return (tuple(t.numel() for t in self._slots.values()), str(self.slot_dtype), self.bucket_bytes, self.depth)
+
+
+def _gather(value, group):
+    out = [None] * dist.get_world_size(group)
+    dist.all_gather_object(out, value, group=group)
+    return out
+
+
+def verify_layout(reducer):
+    """Raise ValueError on EVERY rank when the ranks' reducers would pair buffers of different sizes."""
+    layouts = _gather(reducer.layout(), reducer.group)
+    odd = [r for r, l in enumerate(layouts) if l != layouts[0]]
+    if odd:
+        raise ValueError(f"Data-parallel ranks disagree on gradient slots, bucket size or depth: ranks {odd} differ from rank 0")
+
+
+def replica_digest(model, optimizer=None):
+    """SHA-256 over every parameter and buffer (and, when given, every tensor of the optimizer state) in registration
+    order: equal on all ranks of a healthy data-parallel job after any number of steps."""
+    h = hashlib.sha256()
+
+    def feed(t):
+        t = t.detach()
+        raw = t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+        h.update(str((tuple(t.shape), str(t.dtype))).encode())
+        h.update(raw.contiguous().cpu().reshape(-1).view(torch.uint8).numpy().tobytes())
+
+    for _, t in list(model.named_parameters()) + list(model.named_buffers()):
+        feed(t)
+    if optimizer is not None:
+        for group in optimizer.param_groups:
+            for p in group["params"]:
+                for key, value in sorted(optimizer.state.get(p, {}).items(), key=lambda kv: str(kv[0])):
+                    if torch.is_tensor(value):
+                        feed(value)
+                    else:
+                        h.update(repr((key, value)).encode())
+    return h.hexdigest()
+
+
+def verify_replicas(model, optimizer=None, process_group=None):
+    """Compare replica_digest across ranks; RuntimeError on every rank when they differ.  Call between steps (it copies
+    the state to the host), e.g. after loading a checkpoint on every rank and before writing one."""
+    digests = _gather(replica_digest(model, optimizer), process_group)
+    odd = [r for r, d in enumerate(digests) if d != digests[0]]
+    if odd:
+        raise RuntimeError(f"Data-parallel replicas diverged: ranks {odd} hold different state than rank 0")
+    return digests[0]
+
+
+class PeerWatch:
+    """Host-side liveness check over a gloo control group: `check()` returns when every rank reached it within the
+    timeout and raises RuntimeError naming the missing ranks otherwise.  A rank leaves a job only between steps; the
+    others call check() before their next launch, so no kernel or NCCL collective ever waits for a process that is gone."""
+
+    def __init__(self, timeout_s=30.0, ranks=None):
+        self.timeout = timedelta(seconds=float(timeout_s))
+        self.group = dist.new_group(ranks=ranks, backend="gloo", timeout=self.timeout)
+
+    def check(self):
+        try:
+            dist.monitored_barrier(group=self.group, timeout=self.timeout, wait_all_ranks=True)
+        except RuntimeError as e:
+            raise RuntimeError(f"Data-parallel peer check failed before the step: {e}") from e
+
+
 class _Done:
     def wait(self):
         pass
@@ -161,12 +243,14 @@ class _Both:
         self.second.wait()
 
 
-def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2):
+def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2, peer_timeout=None):
     """Attach a GradientReducer to model.nvfp4_optimizer.  Call after enable_nvfp4 on every rank; rank 0's weights are
     broadcast.  The process group defaults to the world group.  depth: how many later gradients' collectives are started
     before an update waits for its own (captured steps).  bucket_mb: small dense gradients (norm gains, biases) share
     FP32 buckets of this size, one collective each; the weight gradients of converted layers are 19 MB and more each and
-    keep their own collective, written in place by the weight-gradient GEMM (0 gives every gradient its own)."""
+    keep their own collective, written in place by the weight-gradient GEMM (0 gives every gradient its own).
+    peer_timeout: seconds; when given, a PeerWatch is attached as `reducer.watch` and checked at the start of every eager
+    step (call `reducer.watch.check()` yourself between replays of a captured step)."""
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed must be initialised before enable_data_parallel")
     opt = model.nvfp4_optimizer
@@ -177,6 +261,8 @@ def enable_data_parallel(model, process_group=None, *, bucket_mb=25.0, depth=2):
         options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         process_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend="nccl", pg_options=options)
     reducer = GradientReducer(params, process_group, depth=depth, bucket_mb=bucket_mb)
+    verify_layout(reducer)
+    reducer.watch = PeerWatch(peer_timeout) if peer_timeout else None
     opt.reducer = reducer
     from ._backend import quant
     quant._RANK_OFFSET = (reducer.rank * 0x9E3779B1) & 0xFFFFFFFF

@@ -104,3 +104,108 @@ def test_reducer_protocols_on_two_gloo_ranks():
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+# ---- failures are found on the host, between steps ---------------------------------------------------------------------
+def _init(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "sm120-nvfp4-training_b200"))
+    from nvfp4_training import distributed
+    return distributed
+
+
+def _guard_worker(rank, world, port, results):
+    D = _init(rank, world, port)
+    try:
+        seen = {}
+        # mismatched slot sizes: rank 1 converted a layer of another width
+        params = [torch.nn.Parameter(torch.zeros(16 if rank == 0 else 24)), torch.nn.Parameter(torch.zeros(8))]
+        params[0]._v4_request_scale = True
+        try:
+            D.verify_layout(D.GradientReducer(params, slot_dtype=torch.float32))
+        except ValueError as e:
+            seen["layout"] = str(e)
+        # mismatched bucket size alone is found as well
+        same = [torch.nn.Parameter(torch.zeros(16))]
+        same[0]._v4_request_scale = True
+        try:
+            D.verify_layout(D.GradientReducer(same, slot_dtype=torch.float32, bucket_mb=1.0 + rank))
+        except ValueError as e:
+            seen["bucket"] = str(e)
+        D.verify_layout(D.GradientReducer(same, slot_dtype=torch.float32))          # agreeing ranks pass
+        # replicas that hold the same state agree; one changed weight (or moment) is found on every rank
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.LayerNorm(8))
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+        model(torch.ones(2, 8)).sum().backward()
+        opt.step()
+        seen["digest"] = D.verify_replicas(model, opt)
+        if rank == 1:
+            with torch.no_grad():
+                model[0].weight[3, 3] += 1e-3
+        try:
+            D.verify_replicas(model, opt)
+        except RuntimeError as e:
+            seen["diverged"] = str(e)
+        if rank == 1:
+            with torch.no_grad():
+                model[0].weight[3, 3] -= 1e-3
+                opt.state[model[0].bias]["exp_avg"][0] += 1.0
+        try:
+            D.verify_replicas(model, opt)
+        except RuntimeError as e:
+            seen["moment"] = str(e)
+        results[rank] = seen
+    except Exception as e:  # pragma: no cover - reported to the parent
+        results[rank] = repr(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layout_and_replica_guards_raise_on_every_rank():
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_guard_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+    got = dict(results)
+    assert all(isinstance(got[r], dict) for r in (0, 1)), got
+    for r in (0, 1):
+        assert "ranks [1] differ from rank 0" in got[r]["layout"] and "ranks [1] differ" in got[r]["bucket"]
+        assert "ranks [1] hold different state" in got[r]["diverged"] and "ranks [1]" in got[r]["moment"]
+    assert got[0]["digest"] == got[1]["digest"] and len(got[0]["digest"]) == 64
+
+
+def _leaver_worker(rank, world, port, results):
+    D = _init(rank, world, port)
+    try:
+        watch = D.PeerWatch(timeout_s=4.0)
+        watch.check()                      # step 1: everyone is there
+        if rank == world - 1:
+            results[rank] = "left"         # this rank leaves between steps, nothing of its in flight
+            return
+        try:
+            watch.check()                  # step 2: the survivors learn of it before they launch anything
+            results[rank] = "no error"
+        except RuntimeError as e:
+            results[rank] = str(e)
+    except Exception as e:  # pragma: no cover - reported to the parent
+        results[rank] = repr(e)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_survivors_learn_of_a_rank_that_left_between_steps():
+    world = 3
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_leaver_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    got = dict(results)
+    assert got[2] == "left"
+    for r in (0, 1):
+        assert got[r].startswith("Data-parallel peer check failed before the step"), got
+    assert "2" in got[0]                   # rank 0 names the rank that did not answer
