@@ -14,6 +14,7 @@ from .. import _native as nat
 
 # storage format -> (master encoding, variance bits, momentum bits)
 FORMATS = {'tile32': (32, 16, 8), 'fp32_v8': (32, 8, 8), 'split24_v16': (24, 16, 8), 'split24_v8': (24, 8, 8), 'sr16_v8': (16, 8, 8),
+           'split24_m4': (24, 8, 4), 'sr16_m4': (16, 8, 4), 'sr16_m4v4': (16, 4, 4), 'float8_v8': (8, 8, 8),
            'half16_v16': (17, 16, 8), 'half16_v8': (17, 8, 8), 'half16_m8v4': (17, 4, 8), 'half16_m4v4': (17, 4, 4),
            'half16_m4v4_sqrt': (17, 4, 4), 'float8_m4v4_sqrt': (8, 4, 4), 'half16_v8b64': (17, 8, 8), 'half16_v8b128': (17, 8, 8),
            'half16_v8b256': (17, 8, 8)}

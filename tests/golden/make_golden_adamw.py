@@ -16,9 +16,11 @@ def _bits(t):
 
 
 FORMATS = {'tile32': (32, 16, 8), 'split24_v8': (24, 8, 8), 'half16_v8': (17, 8, 8), 'half16_v8b128': (17, 8, 8),
-           'sr16_v8': (16, 8, 8), 'half16_m4v4_sqrt': (17, 4, 4), 'float8_m4v4_sqrt': (8, 4, 4), 'half16_m8v4': (17, 4, 8)}
+           'sr16_v8': (16, 8, 8), 'half16_m4v4_sqrt': (17, 4, 4), 'float8_m4v4_sqrt': (8, 4, 4), 'half16_m8v4': (17, 4, 8),
+           'split24_m4': (24, 8, 4), 'sr16_m4': (16, 8, 4), 'sr16_m4v4': (16, 4, 4), 'float8_v8': (8, 8, 8)}
 LAUNCH = {'tile32': (2, 4), 'split24_v8': (2, 8), 'half16_v8': (8, 8), 'half16_v8b128': (8, 4), 'sr16_v8': (4, 4),
-          'half16_m4v4_sqrt': (1, 4), 'float8_m4v4_sqrt': (2, 4), 'half16_m8v4': (4, 4)}
+          'half16_m4v4_sqrt': (1, 4), 'float8_m4v4_sqrt': (2, 4), 'half16_m8v4': (4, 4),
+          'split24_m4': (2, 4), 'sr16_m4': (4, 8), 'sr16_m4v4': (1, 4), 'float8_v8': (4, 4)}
 
 
 def make_adamw(out):

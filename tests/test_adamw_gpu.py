@@ -9,7 +9,8 @@ from conftest import GOLDEN
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "sr16_v8", "half16_m4v4_sqrt", "float8_m4v4_sqrt", "half16_m8v4"]
+FORMATS = ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "sr16_v8", "half16_m4v4_sqrt", "float8_m4v4_sqrt", "half16_m8v4",
+           "split24_m4", "sr16_m4", "sr16_m4v4", "float8_v8"]
 TORCH_OF = {32: torch.float32, 24: torch.bfloat16, 17: torch.float16, 16: torch.bfloat16, 8: torch.uint8}
 
 

@@ -5,7 +5,8 @@ import pytest
 import oracle as O
 from conftest import GOLDEN
 
-FORMATS = ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "sr16_v8", "half16_m4v4_sqrt", "float8_m4v4_sqrt", "half16_m8v4"]
+FORMATS = ["half16_v8", "half16_v8b128", "split24_v8", "tile32", "sr16_v8", "half16_m4v4_sqrt", "float8_m4v4_sqrt", "half16_m8v4",
+           "split24_m4", "sr16_m4", "sr16_m4v4", "float8_v8"]
 
 
 @pytest.fixture(scope="module")

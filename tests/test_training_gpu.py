@@ -209,3 +209,32 @@ def test_prepack_is_refused_where_the_reference_refuses_it():
         configure(make_model(), "fp4", "half16_v8", prepack=True, remat=True, direct=True)
     with pytest.raises(ValueError, match="FP8 storage"):
         configure(make_model(), "fp4", "float8_m4v4_sqrt", prepack=True, direct=True)
+
+
+@pytest.mark.parametrize("fmt", ["split24_m4", "sr16_m4", "sr16_m4v4", "float8_v8"])
+def test_storage_formats_outside_the_profiles_train(fmt):
+    """The four entries of the reference's FORMATS table that no public profile selects (engine6.py:13-17): configure
+    accepts them, the model trains, state tensors have the reference's dtypes and sizes."""
+    from nvfp4_training._backend.engine import configure
+    from nvfp4_training._backend.optimizer import FORMATS
+    import nvfp4_training as nv
+    master, vb, mb = FORMATS[fmt]
+    from nvfp4_training._backend.linear import AutocastLinear, Linear6
+    model, opt = configure(make_model().cuda(), "fp4", fmt, lr=1e-3)
+    for module in model.modules():          # what prepare_training does after configure: layers run in BF16 under autocast
+        if isinstance(module, Linear6):
+            module.__class__ = AutocastLinear
+    model.nvfp4_optimizer = opt
+    x, y = batch(256)
+    losses = []
+    for _ in range(12):
+        losses.append(nv.train_step(model, mse, x, y).item())
+    nv.check_finite(model)
+    assert losses[-1] < losses[0]
+    w = model[3].weight
+    want = {24: torch.bfloat16, 16: torch.bfloat16, 8: torch.float8_e4m3fn}[master]
+    state = opt.state[w]
+    assert w.dtype == want and ("tail" in state) == (master == 24)
+    n = w.numel()
+    assert state["m"].numel() == ((n + 1) // 2 if mb == 4 and vb != 4 else n)
+    assert ("v" in state) == (vb != 4 or mb != 4)

@@ -24,16 +24,21 @@ def _call_static(native, x, signs, sr, rht, seed, packed, scales, pts):
 def test_static_scratch_variant_matches_the_allocating_entry_point(native):
     g = torch.Generator().manual_seed(42)
     signs = (torch.randint(0, 2, (16,), generator=g).float() * 2 - 1).cuda()
-    cases = [((193, 129), torch.bfloat16, 0, False), ((1024, 2048), torch.bfloat16, native.Q_SR_HASH, True),
-             ((300, 520), torch.float32, native.Q_SR_PHILOX, True)]
+    cases = [((193, 129), torch.bfloat16, 0, False, False), ((1024, 2048), torch.bfloat16, native.Q_SR_HASH, True, False),
+             ((300, 520), torch.float32, native.Q_SR_PHILOX, True, False),
+             ((520, 300), torch.bfloat16, native.Q_SR_HASH, True, True), ((129, 193), torch.float32, 0, False, True)]
     # outputs are allocated by the test up front: the entry point itself never allocates
-    for shape, dtype, sr, rht in cases:
+    # the last flag asks for a transposed view (row stride 1) of a contiguous tensor of the swapped shape
+    for shape, dtype, sr, rht, transposed in cases:
         mp, kp = native.round128(shape[0]), native.round128(shape[1])
         packed = torch.empty((mp, kp // 2), dtype=torch.uint8, device="cuda")
         scales = torch.empty((mp // 128 * 32, kp // 64 * 16), dtype=torch.uint8, device="cuda")
         pts = torch.empty((), dtype=torch.float32, device="cuda")
         for call in range(2):   # two calls in a row: the second one inherits the first one's scratch contents
-            x = (torch.randn(shape, generator=g) * (1.0 + 3.0 * call)).to(dtype).cuda()
+            x = (torch.randn(shape[::-1] if transposed else shape, generator=g) * (1.0 + 3.0 * call)).to(dtype).cuda()
+            if transposed:
+                x = x.t()
+                assert x.stride(0) == 1 and tuple(x.shape) == shape
             want = native.quantize(x, signs, mp, kp, sr, rht, 77 + call)
             packed.fill_(0xCD); scales.fill_(0xCD); pts.fill_(-1.0)
             _call_static(native, x, signs, sr, rht, 77 + call, packed, scales, pts)
