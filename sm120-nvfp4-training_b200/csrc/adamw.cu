@@ -19,6 +19,10 @@
 #include <algorithm>
 #include <cstdlib>
 
+#ifndef ADAM_MIN_BLOCKS
+#define ADAM_MIN_BLOCKS 4   // resident CTAs per SM the update kernel is compiled for (64 registers per thread)
+#endif
+
 namespace nvfp4 {
 
 struct AdamArgs {
@@ -269,6 +273,15 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
     } else {
         uint16_t out[16];
         [[maybe_unused]] int8_t tl[16];
+        // FP16 masters: weights in the subnormal range of FP16 take their own rounding; one test per lane keeps the branch
+        // out of the element loop
+        [[maybe_unused]] bool tiny_any = false;
+        if constexpr (MASTER == 17) {
+            float least = 1.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) least = fminf(least, fabsf(upd[j]));
+            tiny_any = least < 0.00006103515625f;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float u = upd[j];
@@ -281,7 +294,7 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
                 const uint32_t rnd = adam_bits(static_cast<uint32_t>(i0 + j), step, a.key);
                 const uint32_t raw = __float_as_uint(u);
                 uint16_t half = __half_as_ushort(__float2half_rn(__uint_as_float((raw + (rnd & 8191u)) & 0xffffe000u)));
-                if (fabsf(u) < 0.00006103515625f) {
+                if (tiny_any && fabsf(u) < 0.00006103515625f) {
                     const float mag = fabsf(u) * 16777216.f;
                     const float fl = floorf(mag);
                     const float sub = fl + static_cast<float>((static_cast<float>(rnd & 65535u) / 65536.f) < (mag - fl));
@@ -341,8 +354,15 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         mx = seg_max(mx, LANES_B);
         const float sc = fmaxf(mx / 127.f, 1.e-30f);
         int8_t out[16];
+        // |m| <= 127 sc; a quotient under 2^-43 rounds to code 0 whatever its last bits are
+        const SharedDivisor by_sc = shared_divisor(sc);
+        if (by_sc.safe) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) out[j] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(m[j] / sc))));
+            for (int j = 0; j < 16; ++j) out[j] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(by_sc(m[j])))));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) out[j] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(m[j] / sc))));
+        }
         store16(static_cast<int8_t*>(a.m), i0, n, out);
         if (any && (lane & (LANES_B - 1)) == 0) a.ms[blk] = sc;
     }
@@ -384,9 +404,20 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         mx = seg_max(mx, LANES_B);
         const float sc = fmaxf(mx / 255.f, 1.e-30f);
         uint8_t out[16];
+        // root <= 255 sc.  A quotient z under 2^-43 only decides "z * z > 0" below, which turns at z near 2^-75; a nonzero
+        // root = sqrt(v) is at least 2^-75 (v is a float), so sc is at least 1 there and the remainder is normal
+        const SharedDivisor by_sc = shared_divisor(sc);
+        float zq[16];
+        if (by_sc.safe) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) zq[j] = by_sc(root[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) zq[j] = root[j] / sc;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const float z = fminf(255.f, root[j] / sc);
+            const float z = fminf(255.f, zq[j]);
             const float lo = floorf(z);
             const float prob = (z - lo) * (z + lo) / (2.f * lo + 1.f);
             const uint32_t rnd = adam_bits(static_cast<uint32_t>(i0 + j), step, a.key);
@@ -403,8 +434,14 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         mx = seg_max(mx, LANES_B);
         const float sc = fmaxf(mx / 32768.f, 1.e-35f);
         uint16_t out[16];
+        const SharedDivisor by_sc = shared_divisor(sc);     // v <= 32768 sc; a quotient under 2^-43 is zero in FP16
+        if (by_sc.safe) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) out[j] = __half_as_ushort(__float2half_rn(v[j] / sc));
+            for (int j = 0; j < 16; ++j) out[j] = __half_as_ushort(__float2half_rn(by_sc(v[j])));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) out[j] = __half_as_ushort(__float2half_rn(v[j] / sc));
+        }
         store16(static_cast<uint16_t*>(a.v), i0, n, out);
         if (any && (lane & (LANES_B - 1)) == 0) a.vs[blk] = sc;
     }
@@ -434,7 +471,7 @@ __device__ __forceinline__ void adam_publish_scale(const AdamArgs& a, float amax
 }
 
 template <int MASTER, int VB, bool M4, bool NL, int B>
-__global__ void __launch_bounds__(256, 4) adamw_kernel(const AdamArgs a) {
+__global__ void __launch_bounds__(256, ADAM_MIN_BLOCKS) adamw_kernel(const AdamArgs a) {
     float c1 = a.c1, c2 = a.c2;
     uint32_t step = a.step;
     if (a.ctrl) { c1 = a.ctrl[0]; c2 = a.ctrl[1]; step = __float_as_uint(a.ctrl[3]); }

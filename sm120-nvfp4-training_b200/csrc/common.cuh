@@ -124,6 +124,26 @@ __device__ __forceinline__ uint32_t sr_code_signed(float q, uint32_t nh, uint32_
     return shr_mul(f + nh + base, 256u);
 }
 
+// ---- division by a shared divisor -----------------------------------------------------------------
+// Many quotients a / b with one divisor b > 0 (a block's scale).  y = RN(1 / b) is taken once per lane; per quotient
+// q0 = RN(a y), then twice r = a - b q (exact in an FMA), q = RN(q + r y).  The first correction makes q faithful, and with a
+// correctly rounded reciprocal and a faithful quotient the second one returns RN(a / b) (Markstein's theorem on FMA
+// division), as long as no remainder is subnormal.  With b in [2^-60, 2^100] (`safe`) that holds for every quotient of at
+// least 2^-43; every use below has |a / b| <= 32768 and does not depend on the last bits of a quotient under 2^-43
+// (stated at each use).  Outside `safe` the caller divides with `/`.
+struct SharedDivisor {
+    float b, y;
+    bool safe;
+    __device__ __forceinline__ float operator()(float a) const {
+        float q = __fmul_rn(a, y);
+        q = __fmaf_rn(__fmaf_rn(-b, q, a), y, q);
+        return __fmaf_rn(__fmaf_rn(-b, q, a), y, q);
+    }
+};
+__device__ __forceinline__ SharedDivisor shared_divisor(float b) {
+    return SharedDivisor{b, __frcp_rn(b), b >= 8.673617379884035e-19f && b <= 1.2676506002282294e30f};
+}
+
 // ---- scale-factor swizzle (32 x 4 x 4 atom inside 128-row x 4-group blocks) ------------------------
 __host__ __device__ __forceinline__ int64_t scale_offset(int64_t row, int64_t group_col, int64_t groups_per_row) {
     return ((row >> 7) * (groups_per_row >> 2) + (group_col >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
