@@ -68,6 +68,17 @@ __device__ __forceinline__ float byte_as_float(uint32_t word, uint32_t selector)
 }
 __device__ __forceinline__ float u16_as_float(uint32_t x) { return __uint_as_float(0x4B000000u | x) - 8388608.f; }
 
+// u < ((z - lo) * (z + lo)) / (2 lo + 1) for a 16-bit uniform u = k / 65536, without the division: with A the rounded
+// numerator and D = 2 lo + 1, RN(A / D) > u exactly when A - D u > D * (half an ulp of u), and near that boundary the
+// left side is exact in one FMA.  Enumerated against the division over every float z of [0, 255] and the values of k
+// around the turning point (tests/exact_threshold.c).
+__device__ __forceinline__ bool rounds_up(float z, float lo, float u) {
+    const float A = __fmul_rn(z - lo, z + lo);
+    const float D = __fmaf_rn(2.f, lo, 1.f);
+    const int half_ulp = static_cast<int>(__float_as_uint(u) & 0x7f800000u) - (24 << 23);   // negative for u = 0
+    return __fmaf_rn(-D, u, A) > __fmul_rn(D, __int_as_float(max(half_ulp, 0)));
+}
+
 // 16 consecutive items of T starting at element i0; vector loads when the run is complete and aligned.
 template <typename T>
 __device__ __forceinline__ void load16(const T* base, int64_t i0, int64_t n, T (&out)[16], T fill) {
@@ -378,10 +389,9 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         for (int j = 0; j < 16; ++j) {
             const float z = fminf(15.f, root[j] / sc);
             const float lo = floorf(z);
-            const float prob = (z - lo) * (z + lo) / (2.f * lo + 1.f);
             const uint32_t rnd = adam_bits(static_cast<uint32_t>(i0 + j), step, a.key);
             const float uu = static_cast<float>(rnd >> 16) * (1.f / 65536.f);
-            vc[j] = static_cast<uint32_t>(fmaxf(static_cast<float>(root[j] > 0.f), fminf(15.f, lo + static_cast<float>(uu < prob))));
+            vc[j] = static_cast<uint32_t>(fmaxf(static_cast<float>(root[j] > 0.f), fminf(15.f, lo + static_cast<float>(rounds_up(z, lo, uu)))));
         }
         if constexpr (M4) {
             uint8_t out[16];
@@ -419,10 +429,9 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         for (int j = 0; j < 16; ++j) {
             const float z = fminf(255.f, zq[j]);
             const float lo = floorf(z);
-            const float prob = (z - lo) * (z + lo) / (2.f * lo + 1.f);
             const uint32_t rnd = adam_bits(static_cast<uint32_t>(i0 + j), step, a.key);
             const float uu = u16_as_float(rnd >> 16) * (1.f / 65536.f);
-            const float code = fmaxf(root[j] > 0.f ? 1.f : 0.f, lo + (uu < prob ? 1.f : 0.f));
+            const float code = fmaxf(root[j] > 0.f ? 1.f : 0.f, lo + (rounds_up(z, lo, uu) ? 1.f : 0.f));
             out[j] = static_cast<uint8_t>(__float_as_uint(fminf(255.f, code) + 8388608.f));   // integer 0..255 in the low mantissa byte
         }
         store16(static_cast<uint8_t*>(a.v), i0, n, out);
