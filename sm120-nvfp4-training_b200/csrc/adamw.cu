@@ -210,8 +210,8 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
         memcpy(w, raw, 16);
         const float s = any ? a.ms[blk] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)   // int8 -> float as (byte ^ 0x80) - 128
-            m[j] = (byte_as_float(w[j >> 2] ^ 0x80808080u, 0x7650u + (j & 3)) - 128.f) * s;
+        for (int j = 0; j < 16; ++j)   // int8 -> float: (2^23 + (byte ^ 0x80)) - (2^23 + 128), one exact subtraction
+            m[j] = (__uint_as_float(__byte_perm(w[j >> 2] ^ 0x80808080u, 0x4B000000u, 0x7650u + (j & 3))) - 8388736.f) * s;
     }
     if constexpr (VB == 4) {
         const float s = any ? a.vs[i0 / 64] : 0.f;
@@ -262,7 +262,7 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
     if constexpr (MASTER == 32) {
         store16(static_cast<float*>(a.p), i0, n, upd);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) if (i0 + j < n) amax = fmaxf(amax, fabsf(bf16_value(bf16_bits(upd[j]))));
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(bf16_value(bf16_bits(upd[j]))));   // padding updates to zero
     } else if constexpr (MASTER == 8) {
         float peak = 0.f;
 #pragma unroll
@@ -318,7 +318,7 @@ __device__ __forceinline__ float adam_chunk(const AdamArgs& a, int64_t chunk, fl
                 out[j] = static_cast<uint16_t>((__float_as_uint(u) + (rnd & 65535u)) >> 16);
                 hi = bf16_value(out[j]);
             }
-            if (i0 + j < n) amax = fmaxf(amax, fabsf(hi));
+            amax = fmaxf(amax, fabsf(hi));   // elements past the end were loaded as zeros and update to an exact zero
         }
         store16(static_cast<uint16_t*>(a.p), i0, n, out);
         if constexpr (MASTER == 24) store16(a.tail, i0, n, tl);
