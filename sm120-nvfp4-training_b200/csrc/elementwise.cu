@@ -311,16 +311,19 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const uint4* __restric
 }
 
 // The same backward pass with every thread owning CPT fixed groups of eight columns: the dgamma sums stay in registers,
-// four rows are in flight per thread (loads of all four are issued before the first is used) and each row is read once.
+// RB_ROWS rows are in flight per thread (all of their loads are issued before the first is used; two CTAs per SM alternate between
+// loading and computing) and each row is read once.
 // The row-wise dot products are combined through shared memory in a fixed order.  Used when the column count divides
 // evenly over the CTA; the warp-per-row kernel above serves the other shapes.
+constexpr int RB_ROWS = 2;   // rows in flight per thread of the column-owner kernel
+
 template <int CPT>
-__global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ sum,
+__global__ void __launch_bounds__(384, CPT == 1 ? 2 : 1) rmsnorm_bwd_cols_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ sum,
                                                                const float* __restrict__ rstd, const float* __restrict__ gamma,
                                                                const uint4* __restrict__ dres, int64_t rows, int chunks,
                                                                uint4* __restrict__ dx, float* __restrict__ partial,
                                                                float* __restrict__ amax_out) {
-    constexpr int R = 4;
+    constexpr int R = RB_ROWS;
     __shared__ float dots[2][R][12];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
     float w[CPT][8], acc[CPT][8];
@@ -336,7 +339,7 @@ __global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __re
     float best = 0.f;
     int phase = 0;
     for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * R; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * R, phase ^= 1) {
-        uint4 pg[R][CPT], ps[R][CPT];
+        uint4 pg[R][CPT], ps[R][CPT], pd[R][CPT];   // the residual-path gradient is fetched with the other two operands
 #pragma unroll
         for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -345,6 +348,7 @@ __global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __re
                 const bool live = r0 + i < rows;
                 pg[i][k] = live ? dh[at] : make_uint4(0, 0, 0, 0);
                 ps[i][k] = live ? sum[at] : make_uint4(0, 0, 0, 0);
+                pd[i][k] = (live && dres) ? dres[at] : make_uint4(0, 0, 0, 0);
             }
         float rs[R], dot[R];
 #pragma unroll
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __re
                 for (int j = 0; j < 8; ++j) o[j] = rs[i] * (g[j] * w[k][j]) - sv[j] * kf;
                 if (dres) {
                     float d[8];
-                    unpack8(dres[at], d);
+                    unpack8(pd[i][k], d);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) o[j] += d[j];
                 }
@@ -400,12 +404,25 @@ __global__ void __launch_bounds__(384) rmsnorm_bwd_cols_kernel(const uint4* __re
     }
 }
 
+// Column sums of the per-CTA partial rows, in a fixed order: a CTA takes 32 columns, its eight warps take every eighth
+// partial row each, and the eight subtotals are added in warp order.
 __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int parts, int cols, float* __restrict__ out) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= cols) return;
+    __shared__ float subtotal[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + lane;
     float t = 0.f;
-    for (int p = 0; p < parts; ++p) t += partial[static_cast<size_t>(p) * cols + j];
-    out[j] = t;
+    if (j < cols) {
+#pragma unroll 8
+        for (int p = warp; p < parts; p += 8) t += partial[static_cast<size_t>(p) * cols + j];
+    }
+    subtotal[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && j < cols) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += subtotal[w][lane];
+        out[j] = total;
+    }
 }
 
 }  // namespace nvfp4
@@ -447,7 +464,7 @@ static int cols_threads(int64_t cols, int* cpt) {
 
 extern "C" int64_t nvfp4_rmsnorm_bwd_partials(int64_t rows, int64_t cols) {
     int cpt = 0;
-    if (cols_threads(cols, &cpt)) return std::min<int64_t>((rows + 3) / 4, 148 * 2);
+    if (cols_threads(cols, &cpt)) return std::min<int64_t>((rows + RB_ROWS - 1) / RB_ROWS, 148 * 2);
     const int warps = norm_warps(static_cast<int>(cols), 4);
     return std::min<int64_t>((rows + warps - 1) / warps, 148 * 2);
 }
@@ -477,12 +494,12 @@ extern "C" int nvfp4_rmsnorm_bwd(const void* dh, const void* sum, const float* r
         };
         if (cpt == 1) launch(rmsnorm_bwd_cols_kernel<1>);
         else launch(rmsnorm_bwd_cols_kernel<2>);
-        colsum_finish_kernel<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, st>>>(partial, parts, static_cast<int>(cols), dgamma);
+        colsum_finish_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(partial, parts, static_cast<int>(cols), dgamma);
         return launch_status("nvfp4_rmsnorm_bwd");
     }
     rmsnorm_bwd_kernel<<<parts, warps * 32, smem, st>>>(static_cast<const uint4*>(dh), static_cast<const uint4*>(sum), rstd, gamma,
                                                         static_cast<const uint4*>(dres), rows, static_cast<int>(cols / 8),
                                                         static_cast<uint4*>(dx), partial, amax_out);
-    colsum_finish_kernel<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, st>>>(partial, parts, static_cast<int>(cols), dgamma);
+    colsum_finish_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(partial, parts, static_cast<int>(cols), dgamma);
     return launch_status("nvfp4_rmsnorm_bwd");
 }
