@@ -264,6 +264,19 @@ int nvfp4_rmsnorm_bwd(const void* dh, const void* sum, const float* rstd, const 
                       int64_t cols, void* dx, float* partial, float* dgamma, float* amax_out, nvfp4_stream_t stream);
 
 /*
+ * Mean token cross-entropy over BF16 logits [rows][cols] (row pitch in elements; cols a multiple of 8, at most 32768),
+ * int64 targets; FP32 math.  fwd: lse[rows] (kept for the backward pass), row_loss[rows] (scratch), loss = mean over rows,
+ * added in a fixed order.  bwd: dlogits = (softmax - onehot) * grad_out[0] / rows, rounded once to BF16, with max |dlogits|
+ * left in `amax` (nullable) for the quantiser of the output projection's backward.  The reference's benchmark model takes
+ * torch.nn.functional.cross_entropy on an FP32 copy of the logits (src/nvfp4_training/_workloads/lm.py); its optional
+ * Triton loss (token_loss.py) is a different fusion and not what this replaces.
+ */
+int nvfp4_cross_entropy_fwd(const void* logits, int64_t pitch, const int64_t* targets, int64_t rows, int64_t cols, float* lse,
+                            float* row_loss, float* loss, nvfp4_stream_t stream);
+int nvfp4_cross_entropy_bwd(const void* logits, int64_t pitch, const int64_t* targets, const float* lse, const float* grad_out,
+                            int64_t rows, int64_t cols, void* dlogits, int64_t out_pitch, float* amax, nvfp4_stream_t stream);
+
+/*
  * ---- frozen NVFP4 checkpoints in "Comfy" order as LoRA bases ------------------------------------------------------
  * Payload bytes hold the even element in the HIGH nibble; block scales are E4M3 in the same 128 x 4 swizzle as above;
  * one FP32 tensor scale.  These five entry points replace the run-time-compiled kernels the reference launches through

@@ -2,47 +2,11 @@
 // and SwiGLU gating, forward and backward.  Pure HBM-bound streaming kernels: 16-byte vector loads and stores, FP32
 // math, one rounding to BF16 at the end.  They replace chains of 4-6 generic tensor-iterator kernels per use.
 #include "common.cuh"
+#include "bf16x8.cuh"
 
 #include <algorithm>
 
 namespace nvfp4 {
-
-__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&p);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
-// max |v| of non-negative floats through their bit patterns (order-free, hence bit-identical to a separate amax pass)
-__device__ __forceinline__ void atomic_amax(float* dst, float a) {
-    if (dst && a > 0.f) atomicMax(reinterpret_cast<unsigned int*>(dst), __float_as_uint(a));
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
-    return v;
-}
-__device__ __forceinline__ float abs_max8(const uint4& packed) {   // max |bf16| of eight packed values
-    const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
-    uint32_t best = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { best = max(best, w[i] & 0x7fffu); best = max(best, (w[i] >> 16) & 0x7fffu); }
-    return __uint_as_float(best << 16);
-}
 
 // x, out: [tokens = B*S][H][D] BF16 (row pitch `pitch` elements, heads contiguous); cos, sin: [S][D/2] BF16.
 // out[.., j] = a cos - b sin, out[.., j + D/2] = b cos + a sin with (a, b) = (x[.., j], x[.., j + D/2]); sign = -1 inverts.

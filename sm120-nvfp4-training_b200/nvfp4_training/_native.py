@@ -46,6 +46,8 @@ _SIGNATURES = {
     "nvfp4_add_rmsnorm": (I32, [P, P, P, F, I64, I64, P, P, P, P, P]),
     "nvfp4_rmsnorm_bwd_partials": (I64, [I64, I64]),
     "nvfp4_rmsnorm_bwd": (I32, [P, P, P, P, P, I64, I64, P, P, P, P, P]),
+    "nvfp4_cross_entropy_fwd": (I32, [P, I64, P, I64, I64, P, P, P, P]),
+    "nvfp4_cross_entropy_bwd": (I32, [P, I64, P, P, P, I64, I64, P, I64, P, P]),
     "nvfp4_gemm": (I32, [P, P, P, P, P, P, I64, I64, I64, P, I32, P, I32, I64, I64, I64, I32, P, P]),
     "nvfp4_comfy_quantize": (I32, [P, I64, I64, P, I32, U32, P, P, P, P, P, P]),
     "nvfp4_comfy_dequantize": (I32, [P, P, P, P, I64, I64, P]),

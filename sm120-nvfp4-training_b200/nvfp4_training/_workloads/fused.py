@@ -220,3 +220,40 @@ def rope(x, cos, sin):
 
 
 _quant._CAPTURE_EDGE_HOOKS.append(forget_slots)
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets):
+        rows, cols = logits.shape
+        lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        loss = torch.empty((), dtype=torch.float32, device=logits.device)
+        with torch.cuda.device(logits.device):
+            _run("nvfp4_cross_entropy_fwd", logits.data_ptr(), logits.stride(0), targets.data_ptr(), rows, cols, lse.data_ptr(),
+                 row_loss.data_ptr(), loss.data_ptr(), nat.stream_of(logits))
+        ctx.save_for_backward(logits, targets, lse)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        logits, targets, lse = ctx.saved_tensors
+        rows, cols = logits.shape
+        grad_out = grad_out.float().contiguous()
+        dlogits = torch.empty((rows, cols), dtype=torch.bfloat16, device=logits.device)
+        amax = _amax_slot(logits.device)
+        with torch.cuda.device(logits.device):
+            _run("nvfp4_cross_entropy_bwd", logits.data_ptr(), logits.stride(0), targets.data_ptr(), lse.data_ptr(), grad_out.data_ptr(),
+                 rows, cols, dlogits.data_ptr(), cols, amax.data_ptr(), nat.stream_of(logits))
+        return attach_amax(dlogits, amax), None
+
+
+def cross_entropy(logits, targets):
+    """Mean token cross-entropy of BF16 logits [rows, cols] against int64 targets [rows] in two kernels (loss; gradient with
+    its amax), or torch's on an FP32 copy where the shape does not fit them."""
+    rows, cols = logits.shape
+    fits = (logits.is_cuda and logits.dtype == torch.bfloat16 and cols % 8 == 0 and cols <= 32768 and logits.stride(1) == 1
+            and logits.stride(0) % 8 == 0 and logits.data_ptr() % 16 == 0 and targets.dtype == torch.int64)
+    if not fits:
+        return torch.nn.functional.cross_entropy(logits.float(), targets)
+    return _CrossEntropy.apply(logits, targets.contiguous())

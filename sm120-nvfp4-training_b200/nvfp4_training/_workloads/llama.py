@@ -110,8 +110,15 @@ def warm_attention(model, batch, seq, device):
 
 
 def token_loss(model, ids, targets):
+    """Mean next-token cross-entropy.  BF16 logits on the GPU take this library's two loss kernels (no FP32 copy of the
+    logits; the gradient arrives at the output projection with its amax); `reference=True` models and other inputs take
+    torch's cross_entropy on an FP32 copy, as the reference's workload does."""
     logits = model(ids)
-    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
+    flat = logits.reshape(-1, logits.shape[-1])
+    if _fused_ok(flat, getattr(model, "reference", True)):
+        from .fused import cross_entropy
+        return cross_entropy(flat, targets.reshape(-1))
+    return F.cross_entropy(flat.float(), targets.reshape(-1))
 
 
 def linear_parameters(model) -> int:

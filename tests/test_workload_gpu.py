@@ -128,3 +128,31 @@ def test_fused_decoder_matches_the_plain_pytorch_decoder():
     for (name, a), (_, b) in zip(fused.named_parameters(), plain.named_parameters()):
         rel = (a.grad.float() - b.grad.float()).norm() / b.grad.float().norm().clamp_min(1e-12)
         assert rel < 0.06, (name, rel.item())
+
+
+@pytest.mark.parametrize("rows,cols,pitch", [(1000, 32000, 32000), (513, 2048, 2048), (64, 4096, 4352), (7, 8, 8)])
+def test_cross_entropy_matches_torch_on_the_fp32_copy(rows, cols, pitch):
+    """Loss within FP32 rounding of torch's cross_entropy on logits.float(); gradient equal to torch's FP32 gradient rounded
+    to BF16 up to one BF16 ulp (the two exp implementations may differ in the last FP32 bits); amax of the gradient left
+    on the device; a scaled upstream gradient is applied inside the kernel."""
+    from nvfp4_training._backend import quant
+    from nvfp4_training._workloads import fused
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    store = (torch.randn(rows, pitch, device="cuda", generator=g) * 3).bfloat16()
+    targets = torch.randint(0, cols, (rows,), device="cuda", generator=g)
+    got_in = store[:, :cols].detach().requires_grad_(True)
+    want_in = store[:, :cols].detach().clone().requires_grad_(True)
+    hook = {}
+    got_in.register_hook(lambda grad: hook.update(amax=quant.known_amax(grad)))
+    loss = fused.cross_entropy(got_in, targets)
+    (loss * 3).backward()
+    want = F.cross_entropy(want_in.float(), targets)
+    (want * 3).backward()
+    assert abs(loss.item() - want.item()) <= 2e-6 * abs(want.item())
+    a, b = got_in.grad.float(), want_in.grad.float()
+    assert got_in.grad.dtype == torch.bfloat16
+    ulp = b.abs().clamp_min(1e-30) * 2.0 ** -7
+    assert bool(((a - b).abs() <= ulp).all())
+    assert float((a != b).float().mean()) < 0.02
+    if hook.get("amax") is not None:
+        assert hook["amax"][0].item() == a.abs().max().item()
