@@ -254,6 +254,11 @@ int nvfp4_split_init(const float* src, int64_t n, int master, void* hi, int8_t* 
  */
 int nvfp4_rope(const void* x, void* out, const void* cos_t, const void* sin_t, int64_t tokens, int seq, int heads, int dim,
                int64_t pitch, int64_t out_pitch, int mode, float* amax, nvfp4_stream_t stream);
+/* The backward pass of nvfp4_rope over a fused q / k / v projection in one launch: dqkv [tokens][3 * heads * dim] receives the
+ * inverse rotation of dq and dk and a copy of dv (each [tokens][heads][dim] with its own row pitch); amax as above. */
+int nvfp4_rope_qkv_bwd(const void* dq, int64_t dq_pitch, const void* dk, int64_t dk_pitch, const void* dv, int64_t dv_pitch,
+                       void* dqkv, const void* cos_t, const void* sin_t, int64_t tokens, int seq, int heads, int dim,
+                       float* amax, nvfp4_stream_t stream);
 int nvfp4_swiglu(const void* gate, int64_t gate_pitch, const void* up, int64_t up_pitch, const void* dout, int64_t dout_pitch,
                  void* out_or_dgate, int64_t out_pitch, void* dup, int64_t dup_pitch, int64_t rows, int64_t cols, float* amax,
                  nvfp4_stream_t stream);

@@ -12,10 +12,20 @@ namespace nvfp4 {
 // out[.., j] = a cos - b sin, out[.., j + D/2] = b cos + a sin with (a, b) = (x[.., j], x[.., j + D/2]); sign = -1 inverts.
 // sign = 0 copies (the third projection of a fused q / k / v gradient, which is not rotated).  amax (nullable) receives
 // max |out|.
-__global__ void __launch_bounds__(256) rope_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
-                                                   const uint16_t* __restrict__ cos_t, const uint16_t* __restrict__ sin_t,
-                                                   int64_t tokens, int seq, int heads, int dim, int64_t pitch, int64_t out_pitch,
-                                                   float sign, float* __restrict__ amax) {
+// Up to three tensors per launch (blockIdx.y picks one): the gradients of q, k and v go into one fused tensor this way.
+struct RopeJobs {
+    const uint16_t* x[3];
+    uint16_t* out[3];
+    int64_t pitch[3];
+    float sign[3];
+};
+__global__ void __launch_bounds__(256) rope_kernel(const RopeJobs jobs, const uint16_t* __restrict__ cos_t,
+                                                   const uint16_t* __restrict__ sin_t, int64_t tokens, int seq, int heads, int dim,
+                                                   int64_t out_pitch, float* __restrict__ amax) {
+    const uint16_t* __restrict__ x = jobs.x[blockIdx.y];
+    uint16_t* __restrict__ out = jobs.out[blockIdx.y];
+    const int64_t pitch = jobs.pitch[blockIdx.y];
+    const float sign = jobs.sign[blockIdx.y];
     float best = 0.f;
     const int half = dim >> 1, chunks = half >> 3;   // 8 elements per thread from each half
     const int64_t total = tokens * heads * chunks;
@@ -125,10 +135,39 @@ extern "C" int nvfp4_rope(const void* x, void* out, const void* cos_t, const voi
     for (const void* p : {x, static_cast<const void*>(out), cos_t, sin_t})
         NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_rope: pointers must be 16-byte aligned");
     const int64_t items = tokens * heads * (dim / 16);
+    RopeJobs jobs{};
+    jobs.x[0] = static_cast<const uint16_t*>(x); jobs.out[0] = static_cast<uint16_t*>(out); jobs.pitch[0] = pitch;
+    jobs.sign[0] = mode == 0 ? 1.f : mode == 1 ? -1.f : 0.f;
     rope_kernel<<<stream_grid(items), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), static_cast<const uint16_t*>(cos_t),
-        static_cast<const uint16_t*>(sin_t), tokens, seq, heads, dim, pitch, out_pitch, mode == 0 ? 1.f : mode == 1 ? -1.f : 0.f, amax);
+        jobs, static_cast<const uint16_t*>(cos_t), static_cast<const uint16_t*>(sin_t), tokens, seq, heads, dim, out_pitch, amax);
     return launch_status("nvfp4_rope");
+}
+
+extern "C" int nvfp4_rope_qkv_bwd(const void* dq, int64_t dq_pitch, const void* dk, int64_t dk_pitch, const void* dv, int64_t dv_pitch,
+                                  void* dqkv, const void* cos_t, const void* sin_t, int64_t tokens, int seq, int heads, int dim,
+                                  float* amax, nvfp4_stream_t stream) {
+    NVFP4_REQUIRE(dq && dk && dv && dqkv && cos_t && sin_t, NVFP4_ERR_ARG, "nvfp4_rope_qkv_bwd: null pointer");
+    const int64_t width = static_cast<int64_t>(heads) * dim;
+    NVFP4_REQUIRE(tokens > 0 && seq > 0 && heads > 0 && dim > 0 && dim % 16 == 0, NVFP4_ERR_ARG,
+                  "nvfp4_rope_qkv_bwd: head dimension must be a multiple of 16");
+    for (int64_t pitch : {dq_pitch, dk_pitch, dv_pitch})
+        NVFP4_REQUIRE(pitch >= width && pitch % 8 == 0, NVFP4_ERR_ARG, "nvfp4_rope_qkv_bwd: row pitches must be multiples of 8, at least heads * dim");
+    for (const void* p : {dq, dk, dv, static_cast<const void*>(dqkv), cos_t, sin_t})
+        NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0, NVFP4_ERR_ALIGN, "nvfp4_rope_qkv_bwd: pointers must be 16-byte aligned");
+    RopeJobs jobs{};
+    const void* src[3] = {dq, dk, dv};
+    const int64_t pitches[3] = {dq_pitch, dk_pitch, dv_pitch};
+    for (int i = 0; i < 3; ++i) {
+        jobs.x[i] = static_cast<const uint16_t*>(src[i]);
+        jobs.out[i] = static_cast<uint16_t*>(dqkv) + width * i;
+        jobs.pitch[i] = pitches[i];
+        jobs.sign[i] = i < 2 ? -1.f : 0.f;          // inverse rotation of dq and dk, copy of dv
+    }
+    const int64_t items = tokens * heads * (dim / 16);
+    dim3 grid(stream_grid(items), 3);
+    rope_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        jobs, static_cast<const uint16_t*>(cos_t), static_cast<const uint16_t*>(sin_t), tokens, seq, heads, dim, 3 * width, amax);
+    return launch_status("nvfp4_rope_qkv_bwd");
 }
 
 extern "C" int nvfp4_swiglu(const void* gate, int64_t gate_pitch, const void* up, int64_t up_pitch, const void* dout, int64_t dout_pitch,

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "nvfp4_adamw_plain": (I32, [P, P, P, P, I64, F, F, F, F, F, F, F, F, P, P]),
     "nvfp4_split_init": (I32, [P, I64, I32, P, P, P]),
     "nvfp4_rope": (I32, [P, P, P, P, I64, I32, I32, I32, I64, I64, I32, P, P]),
+    "nvfp4_rope_qkv_bwd": (I32, [P, I64, P, I64, P, I64, P, P, P, I64, I32, I32, I32, P, P]),
     "nvfp4_swiglu": (I32, [P, I64, P, I64, P, I64, P, I64, P, I64, I64, I64, P, P]),
     "nvfp4_add_rmsnorm": (I32, [P, P, P, F, I64, I64, P, P, P, P, P]),
     "nvfp4_rmsnorm_bwd_partials": (I64, [I64, I64]),

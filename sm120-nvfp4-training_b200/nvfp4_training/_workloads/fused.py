@@ -173,12 +173,11 @@ class _RopeAttention(torch.autograd.Function):
         ctx.inner = ctx.leaves = None
         dqkv = torch.empty((b, s, 3 * width), dtype=grad.dtype, device=grad.device)
         amax = _amax_slot(grad.device)
+        parts = [t if (t.stride(3) == 1 and t.stride(2) == d and t.stride(0) == s * t.stride(1)) else t.contiguous() for t in (dq, dk, dv)]
         with torch.cuda.device(grad.device):
-            for i, (t, mode) in enumerate(((dq, 1), (dk, 1), (dv, 2))):
-                if t.stride(3) != 1 or t.stride(2) != d or t.stride(0) != s * t.stride(1):
-                    t = t.contiguous()
-                _run("nvfp4_rope", t.data_ptr(), dqkv.data_ptr() + 2 * width * i, cos.data_ptr(), sin.data_ptr(), b * s, s, heads, d,
-                     t.stride(1), 3 * width, mode, amax.data_ptr(), nat.stream_of(grad))
+            _run("nvfp4_rope_qkv_bwd", parts[0].data_ptr(), parts[0].stride(1), parts[1].data_ptr(), parts[1].stride(1),
+                 parts[2].data_ptr(), parts[2].stride(1), dqkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), b * s, s, heads, d,
+                 amax.data_ptr(), nat.stream_of(grad))
         return attach_amax(dqkv, amax), None, None, None
 
 
