@@ -258,8 +258,8 @@ C2 = dict(tokens=8192, d_in=4096, d_out=4096)
 FP4_NOMINAL_TFLOPS = 9000.0
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures summarised under profiles/
 # (one capture per kernel; outputs still resident in the 126 MB L2 at kernel end are not in them)
-NCU_TRAFFIC = {"gemm_c2": (50.2e6 + 50.6e6 + 42.3e6) / 3, "quant_c1": 33.6e6, "adamw": 293.5e6}
-NCU_TRAFFIC_SOURCE = {"gemm_c2": "profiles/gemm_kernel_c2.md", "quant_c1": "profiles/quant_tile_kernel_c1.md",
+NCU_TRAFFIC = {"gemm_c2": (50.2e6 + 50.6e6 + 42.3e6) / 3, "quant_c1": 33.6e6, "adamw": 287.1e6}
+NCU_TRAFFIC_SOURCE = {"gemm_c2": "profiles/gemm_kernel_c2.md", "quant_c1": "profiles/quant_stream_kernel_c1.md",
                       "adamw": "profiles/adamw_kernel_balanced.md"}
 
 
