@@ -359,7 +359,7 @@ def build_c3(cfg, world, device):
     model = nv.enable_nvfp4(model, profile="balanced", lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
     model.nvfp4_optimizer.param_groups[0]["prepack"] = os.environ.get("NVFP4_PREPACK", "0") == "1"
     if world > 1:
-        nv.enable_data_parallel(model)
+        nv.enable_data_parallel(model, depth=int(os.environ.get("NVFP4_DP_DEPTH", "2")))
     return model
 
 

@@ -107,6 +107,11 @@ def test_update_matches_oracle_on_ragged_sizes(native, fmt, n):
     scale = torch.zeros(1, device="cuda")
     for t in (1, 2):
         grad = (torch.randn(n, generator=g) * (3e-3 if t == 1 else 50.0)).bfloat16()
+        # state blocks whose scale leaves the range of the shared-reciprocal division (all-zero gradients: scale 1e-30;
+        # gradients near 1e-14: scale about 1e-17) and one far up the range
+        grad[:1024] = 0
+        grad[1024:2048] *= 1e-12
+        grad[2048:2560] *= 1e12
         h = O.adam_hyper(3e-4, (0.9, 0.95), 1e-8, 0.1, t)
         native.adamw_step(p, master, grad.cuda(), m, v, ms, vs, vbits=vb, mbits=mb, nonlinear_m=fmt.endswith("_sqrt"),
                           state_block=O.state_block(fmt), hyper=h, step=t, key=777, tail=tail, unit=unit, scale_out=scale)
