@@ -34,6 +34,24 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
     return v;
 }
+// One atomic per warp: for kernels whose few, long-running CTAs would otherwise wait for their slowest warp at the end.
+__device__ __forceinline__ void warp_atomic_amax(float* dst, float best) {
+    best = warp_max(best);
+    if ((threadIdx.x & 31) == 0) atomic_amax(dst, best);
+}
+// One atomic per CTA: tens of thousands of same-address atomics (one per warp) serialise in the L2 and were measured to
+// cost more than the kernel's data movement.  Every thread of the CTA must call it.
+__device__ __forceinline__ void block_atomic_amax(float* dst, float best) {
+    __shared__ float warp_best[32];
+    best = warp_max(best);
+    if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float b = threadIdx.x < ((blockDim.x + 31) >> 5) ? warp_best[threadIdx.x] : 0.f;
+        b = warp_max(b);
+        if (threadIdx.x == 0) atomic_amax(dst, b);
+    }
+}
 __device__ __forceinline__ float abs_max8(const uint4& packed) {   // max |bf16| of eight packed values
     const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
     uint32_t best = 0;

@@ -22,10 +22,11 @@ struct RopeJobs {
 __global__ void __launch_bounds__(256) rope_kernel(const RopeJobs jobs, const uint16_t* __restrict__ cos_t,
                                                    const uint16_t* __restrict__ sin_t, int64_t tokens, int seq, int heads, int dim,
                                                    int64_t out_pitch, float* __restrict__ amax) {
-    const uint16_t* __restrict__ x = jobs.x[blockIdx.y];
-    uint16_t* __restrict__ out = jobs.out[blockIdx.y];
-    const int64_t pitch = jobs.pitch[blockIdx.y];
-    const float sign = jobs.sign[blockIdx.y];
+    const int job = blockIdx.y;        // selected with conditionals: indexing a by-value struct would copy it to local memory
+    const uint16_t* __restrict__ x = job == 0 ? jobs.x[0] : job == 1 ? jobs.x[1] : jobs.x[2];
+    uint16_t* __restrict__ out = job == 0 ? jobs.out[0] : job == 1 ? jobs.out[1] : jobs.out[2];
+    const int64_t pitch = job == 0 ? jobs.pitch[0] : job == 1 ? jobs.pitch[1] : jobs.pitch[2];
+    const float sign = job == 0 ? jobs.sign[0] : job == 1 ? jobs.sign[1] : jobs.sign[2];
     float best = 0.f;
     const int half = dim >> 1, chunks = half >> 3;   // 8 elements per thread from each half
     const int64_t total = tokens * heads * chunks;
@@ -56,10 +57,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeJobs jobs, const ui
         *reinterpret_cast<uint4*>(out + obase + half) = pb;
         if (amax) best = fmaxf(best, fmaxf(abs_max8(pa), abs_max8(pb)));
     }
-    if (amax) {
-        best = warp_max(best);
-        if ((threadIdx.x & 31) == 0) atomic_amax(amax, best);
-    }
+    if (amax) block_atomic_amax(amax, best);
 }
 
 // gate, up, out (and dout, dgate, dup): [rows][cols] BF16 with their own row pitches (elements, multiples of 8), so that
@@ -82,10 +80,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(Rows gate, Rows up, Row
         *reinterpret_cast<uint4*>(out.p + r * out.pitch + c) = packed;
         best = fmaxf(best, abs_max8(packed));
     }
-    if (amax) {
-        best = warp_max(best);
-        if ((threadIdx.x & 31) == 0) atomic_amax(amax, best);
-    }
+    if (amax) block_atomic_amax(amax, best);
 }
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(Rows gate, Rows up, Rows dout, RowsOut dgate, RowsOut dup, int64_t rows, int chunks,
                                                          float* __restrict__ amax) {
@@ -110,10 +105,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(Rows gate, Rows up, Row
         *reinterpret_cast<uint4*>(dup.p + r * dup.pitch + c) = pu;
         best = fmaxf(best, fmaxf(abs_max8(pg), abs_max8(pu)));
     }
-    if (amax) {
-        best = warp_max(best);
-        if ((threadIdx.x & 31) == 0) atomic_amax(amax, best);
-    }
+    if (amax) warp_atomic_amax(amax, best);   // measured: 118.6 us against 125.2 us with the CTA-level form, which helps the other kernels
 }
 
 static unsigned stream_grid(int64_t work_items) {
@@ -243,8 +235,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const uint4* __res
         }
         __syncwarp();
     }
-    best = warp_max(best);
-    if (lane == 0) atomic_amax(amax_out, best);
+    warp_atomic_amax(amax_out, best);
 }
 
 // Backward of h = sum * rstd * gamma for one warp per row, plus the gradient that arrives on the residual path:
@@ -303,8 +294,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const uint4* __restric
             best = fmaxf(best, abs_max8(packed));
         }
     }
-    best = warp_max(best);
-    if (lane == 0) atomic_amax(amax_out, best);
+    block_atomic_amax(amax_out, best);
     __syncthreads();
     for (int j = threadIdx.x; j < cols; j += blockDim.x) {
         float t = 0.f;
@@ -397,8 +387,7 @@ __global__ void __launch_bounds__(384, CPT == 1 ? 2 : 1) rmsnorm_bwd_cols_kernel
             }
         }
     }
-    best = warp_max(best);
-    if (lane == 0) atomic_amax(amax_out, best);
+    block_atomic_amax(amax_out, best);
 #pragma unroll
     for (int k = 0; k < CPT; ++k) {
         float* dst = partial + static_cast<size_t>(blockIdx.x) * chunks * 8 + static_cast<size_t>(tid + k * blockDim.x) * 8;

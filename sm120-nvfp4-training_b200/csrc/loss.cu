@@ -116,8 +116,7 @@ __global__ void __launch_bounds__(CE_THREADS, 2) ce_backward_kernel(const uint16
         reinterpret_cast<uint4*>(dlogits + r * out_pitch)[at] = packed;
         best = fmaxf(best, abs_max8(packed));
     }
-    best = warp_max(best);
-    if ((threadIdx.x & 31) == 0) atomic_amax(amax, best);
+    block_atomic_amax(amax, best);
 }
 
 }  // namespace nvfp4
