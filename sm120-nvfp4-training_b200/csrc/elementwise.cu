@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(Rows gate, Rows up, Row
         unpack8(*reinterpret_cast<const uint4*>(gate.p + r * gate.pitch + c), g);
         unpack8(*reinterpret_cast<const uint4*>(up.p + r * up.pitch + c), u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+        for (int j = 0; j < 8; ++j) o[j] = __fdividef(g[j], 1.f + __expf(-g[j])) * u[j];   // result is rounded to BF16: the fast quotient's 2 ulp do not show
         const uint4 packed = pack8(o);
         *reinterpret_cast<uint4*>(out.p + r * out.pitch + c) = packed;
         best = fmaxf(best, abs_max8(packed));
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(Rows gate, Rows up, Row
         unpack8(*reinterpret_cast<const uint4*>(dout.p + r * dout.pitch + c), d);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float sg = 1.f / (1.f + __expf(-g[j]));
+            const float sg = __fdividef(1.f, 1.f + __expf(-g[j]));
             const float silu = g[j] * sg;
             du[j] = d[j] * silu;
             dg[j] = d[j] * u[j] * (sg + silu * (1.f - sg));
