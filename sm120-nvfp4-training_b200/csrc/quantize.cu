@@ -1,9 +1,10 @@
 // NVFP4 quantiser for sm_100a: tensor amax, the two tile quantisers (row packing and/or transposed packing from one
 // read of the source), dequantiser.  The group arithmetic and its numerical contract live in quant_core.cuh.
 //
-//   quant_stream_kernel  persistent, warp-specialised: one warp streams 128 x 128 source tiles into a shared-memory ring
-//                        with TMA loads (out-of-range rows / columns arrive as zeros); eight warps encode from shared
-//                        memory, each into its own staging slabs, which leave by TMA stores.
+//   quant_stream_kernel  persistent: 128 x 128 source tiles stream into a shared-memory ring by TMA loads (out-of-range
+//                        rows / columns arrive as zeros); eight warps encode from shared memory, each into its own staging
+//                        slabs, which leave by TMA stores; the ring is refilled by the last warp to finish a stage or, in
+//                        the hash mode, by a ninth warp.
 //                        Serves 2-byte sources with unit column stride and 16-byte aligned rows.
 //   quant_tile_kernel    one 128 x 128 tile per CTA with per-thread loads: every other source (FP32, E4M3 x unit,
 //                        arbitrary strides, unaligned bases).
@@ -336,7 +337,12 @@ static int launch_tile(const void* x, int64_t rows, int64_t cols, int64_t rs, in
 // ================================================================================================
 constexpr int QS_STAGES = 2;            // source tiles in flight per CTA (two CTAs per SM: four per SM, 128 KB)
 constexpr int QS_COMPUTE_WARPS = 8;
-constexpr int QS_THREADS = QS_COMPUTE_WARPS * 32 + 32;   // + the loading warp
+// Two ways to keep the ring full.  LOADER: a ninth warp waits for a stage's `empty` barrier and issues the next load (288
+// threads, 96 registers per thread).  Without it the last encoding warp to finish with a stage issues the load itself (256
+// threads, which leaves 128 registers per thread: no spills).  Measured on both packings of 8192 x 4096: Philox 40.0 -> 36.9
+// us without the loader, the reference's hash generator 97.9 -> 110 us; round to nearest the same.  So hash keeps the loader.
+__host__ __device__ constexpr bool qs_loader(int sr) { return sr == SR_HASH; }
+__host__ __device__ constexpr int qs_threads(int sr) { return QS_COMPUTE_WARPS * 32 + (qs_loader(sr) ? 32 : 0); }
 constexpr int QS_TILE_BYTES = TILE * TILE * 2;
 constexpr int QS_SLAB = TILE / QS_COMPUTE_WARPS;          // 16 packing rows per warp and orientation
 
@@ -357,7 +363,8 @@ struct __align__(128) StreamSmem {
     uint16_t in[STAGES][TR * TILE];        // dense rows of 256 bytes, as the tile load writes them
     WarpStage stage[QS_COMPUTE_WARPS];
     uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t empty[STAGES];                // LOADER: the eight warps have finished reading the stage's tile
+    unsigned int released[STAGES];         // without LOADER: count of warps that have finished with it
     int abort;
 };
 
@@ -389,7 +396,7 @@ __device__ __forceinline__ void unpack16(const uint4 a, const uint4 b, float (&v
 // The tile loop of one encoding warp.  FAST selects the division-free scale arithmetic; it is decided once per launch from
 // the tensor scales, so no group pays for a branch.
 template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT, bool FAST, int TR>
-__device__ __forceinline__ void stream_encode_loop(StreamSmem<TR>& S, const CUtensorMap* map_row, const CUtensorMap* map_col,
+__device__ __forceinline__ void stream_encode_loop(StreamSmem<TR>& S, const CUtensorMap* map_in, const CUtensorMap* map_row, const CUtensorMap* map_col,
                                                    const StreamArgs& a, const float (&sg)[16], float inv_r, float inv_c,
                                                    int warp, int lane) {
     using namespace aop;
@@ -476,7 +483,21 @@ __device__ __forceinline__ void stream_encode_loop(StreamSmem<TR>& S, const CUte
         // engine and to the lanes that store the scale pieces
         fence_async_shared();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&S.empty[s]);
+        if constexpr (qs_loader(SR)) {
+            if (lane == 0) mbar_arrive(&S.empty[s]);
+        } else if (lane == 0) {
+            // the last of the eight warps to finish with this stage loads the tile that will use it next
+            if (atomicAdd(&S.released[s], 1u) == QS_COMPUTE_WARPS - 1) {
+                atomicExch(&S.released[s], 0u);
+                const int next = t + STAGES * static_cast<int>(gridDim.x);
+                if (next < n_tiles) {
+                    const int nrt = next / a.tiles_c, nct = next - nrt * a.tiles_c;
+                    fence_async_shared();
+                    mbar_expect_tx(&S.full[s], TR * TILE * 2);
+                    tma_load_2d(S.in[s], map_in, nct * TILE, nrt * TR, &S.full[s]);
+                }
+            }
+        }
         if constexpr (ROW) {
             if (SLAB == QS_SLAB || lane < 2 * SLAB) {
                 const int prow = rt * TR + slab + (lane >> 1);     // packing row of this piece; 128 of them share a block
@@ -504,11 +525,10 @@ __device__ __forceinline__ void stream_encode_loop(StreamSmem<TR>& S, const CUte
 // Every encoding warp works on its own: of each 128 x 128 source tile it takes packing rows 16w .. 16w+15 of the row
 // orientation (source rows) and of the transposed orientation (source columns), stages the 1 KB payload slabs in its own
 // shared memory, hands them to the copy engine (one TMA store per slab) and writes its scale bytes as 4-byte pieces of the
-// swizzled blocks.  The only block-wide events are the ring's full / empty barriers.
+// swizzled blocks.  The only block-wide events are the ring's full barriers and the per-stage release counters.
 template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT, int TR>
-__global__ void __launch_bounds__(QS_THREADS, 2)
-quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_row,
-                    const __grid_constant__ CUtensorMap map_col, const StreamArgs a) {
+__device__ __forceinline__ void quant_stream_body(const CUtensorMap& map_in, const CUtensorMap& map_row, const CUtensorMap& map_col,
+                                                  const StreamArgs& a) {
     using namespace aop;
     using Smem = StreamSmem<TR>;
     extern __shared__ __align__(128) uint8_t stream_smem_raw[];
@@ -517,13 +537,22 @@ quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_con
     const int n_tiles = a.tiles_r * a.tiles_c;
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < Smem::STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], QS_COMPUTE_WARPS); }
+        for (int s = 0; s < Smem::STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], QS_COMPUTE_WARPS); S.released[s] = 0u; }
         S.abort = 0;
         fence_barrier_init();
+        if constexpr (!qs_loader(SR)) {
+            // the first tiles of this CTA; later ones are requested by the warp that frees a stage
+            for (int s = 0; s < Smem::STAGES; ++s) {
+                const int t = blockIdx.x + s * static_cast<int>(gridDim.x);
+                if (t >= n_tiles) break;
+                const int rt = t / a.tiles_c, ct = t - rt * a.tiles_c;
+                mbar_expect_tx(&S.full[s], TR * TILE * 2);
+                tma_load_2d(S.in[s], &map_in, ct * TILE, rt * TR, &S.full[s]);
+            }
+        }
     }
     __syncthreads();
-
-    if (warp == QS_COMPUTE_WARPS) {
+    if (qs_loader(SR) && warp == QS_COMPUTE_WARPS) {
         // ---- loading warp: keeps the ring full --------------------------------------------------------------------
         int it = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
@@ -540,7 +569,6 @@ quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_con
             __syncwarp();
         }
     } else {
-        // ---- encoding warps -------------------------------------------------------------------------------------
         float sg[16];
 #pragma unroll
         for (int l = 0; l < 16; ++l) sg[l] = a.signs ? __ldg(a.signs + l) : 1.f;
@@ -549,12 +577,19 @@ quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_con
         if constexpr (ROW) sm_r = scale_math(tensor_scale(a.amax, a.R.pts, R_RHT, writer));
         if constexpr (COL) sm_c = scale_math(tensor_scale(a.amax, a.C.pts, C_RHT, writer));
         if (sm_r.fast && sm_c.fast)
-            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, true, TR>(S, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
+            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, true, TR>(S, &map_in, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
         else
-            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, false, TR>(S, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
+            stream_encode_loop<DT, ROW, COL, SR, R_RHT, C_RHT, false, TR>(S, &map_in, &map_row, &map_col, a, sg, sm_r.inv, sm_c.inv, warp, lane);
     }
     __syncthreads();
     if (tid == 0 && S.abort && a.status) *a.status = NVFP4_ERR_TIMEOUT;
+}
+
+template <int DT, bool ROW, bool COL, int SR, bool R_RHT, bool C_RHT, int TR>
+__global__ void __launch_bounds__(qs_threads(SR), 2)
+quant_stream_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_row,
+                    const __grid_constant__ CUtensorMap map_col, const StreamArgs a) {
+    quant_stream_body<DT, ROW, COL, SR, R_RHT, C_RHT, TR>(map_in, map_row, map_col, a);
 }
 
 static bool stream_enabled() {
@@ -573,14 +608,14 @@ static cudaError_t launch_stream_one(const CUtensorMap& mi, const CUtensorMap& m
                                      int grid, cudaStream_t st) {
     constexpr int TR = COL ? TILE : QS_ROW_ONLY_TILE_ROWS;
     const size_t smem = sizeof(StreamSmem<TR>);
+    auto kernel = quant_stream_kernel<DT, ROW, COL, SR, R_RHT, C_RHT, TR>;
     static bool configured = false;   // one flag per kernel instantiation; the attribute belongs to the function
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(quant_stream_kernel<DT, ROW, COL, SR, R_RHT, C_RHT, TR>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    quant_stream_kernel<DT, ROW, COL, SR, R_RHT, C_RHT, TR><<<grid, QS_THREADS, smem, st>>>(mi, mr, mc, a);
+    kernel<<<grid, qs_threads(SR), smem, st>>>(mi, mr, mc, a);
     return cudaSuccess;
 }
 
