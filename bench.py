@@ -551,10 +551,23 @@ def cpu_layer_seconds(cfg, budget_tokens):
     return t_lin, t_adam
 
 
+def use_all_host_cores():
+    """Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU legs are meant to use every core.  The oracle links the
+    system's OpenMP runtime, which torch.set_num_threads does not reach, so that runtime is told directly as well."""
+    import ctypes
+    n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(n)
+    except OSError:
+        pass
+    return n
+
+
 def cpu_train_baseline(cfg, budget_tokens=CPU_BUDGET_TOKENS, samples=3):
     """The oracle on the host cores, median of `samples` runs of one layer, extrapolated to the full token count and layer
     count.  Attention, norms, embedding and head are not included: an optimistic CPU figure."""
-    torch.set_num_threads(os.cpu_count() or 1)
+    use_all_host_cores()
     tokens_full = cfg["micro_batch"] * cfg["seq"]
     runs = sorted(cpu_layer_seconds(cfg, budget_tokens) for _ in range(samples))
     t_lin, t_adam = runs[len(runs) // 2]
