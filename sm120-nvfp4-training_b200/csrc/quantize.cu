@@ -931,10 +931,12 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     const uint32_t w[2] = {p.x, p.y};
     float v[16];
 #pragma unroll
-    for (int l = 0; l < 16; ++l) {
-        const uint32_t byte = (w[l >> 3] >> (8 * ((l >> 1) & 3))) & 0xffu;
-        const uint32_t code = ((l & 1) ^ (hi_first ? 1 : 0)) ? (byte >> 4) : (byte & 15u);
-        v[l] = __fmul_rn(__fmul_rn(e2m1_to_float(code), s), t);
+    for (int b = 0; b < 8; ++b) {
+        // both codes of a byte in one conversion (e2m1 values are exact in FP16); .x is the low nibble
+        const __half2_raw pair = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((w[b >> 2] >> (8 * (b & 3))) & 0xffu), __NV_E2M1);
+        const float lo = __half2float(__ushort_as_half(pair.x)), hi = __half2float(__ushort_as_half(pair.y));
+        v[2 * b] = __fmul_rn(__fmul_rn(hi_first ? hi : lo, s), t);
+        v[2 * b + 1] = __fmul_rn(__fmul_rn(hi_first ? lo : hi, s), t);
     }
     const int64_t c0 = g * 16;
     if (vec_ok && c0 + 16 <= cols) {
