@@ -245,8 +245,10 @@ __global__ void __launch_bounds__(256) comfy_transpose_kernel(const uint8_t* __r
             for (int j = 0; j < 8; ++j) {
                 const uint32_t byte = (w[grp * 2 + (j >> 2)] >> (8 * (j & 3))) & 0xffu;
                 const int kk = grp * 16 + j * 2;
-                column[kk * TP] = static_cast<uint16_t>(bf16_rne_bits(e2m1_to_float(byte >> 4) * sc) ^ flip);
-                column[(kk + 1) * TP] = static_cast<uint16_t>(bf16_rne_bits(e2m1_to_float(byte & 15u) * sc) ^ flip);
+                // both codes of the byte in one conversion (exact in FP16); .x is the low nibble, the odd element here
+                const __half2_raw pair = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+                column[kk * TP] = static_cast<uint16_t>(bf16_rne_bits(__half2float(__ushort_as_half(pair.y)) * sc) ^ flip);
+                column[(kk + 1) * TP] = static_cast<uint16_t>(bf16_rne_bits(__half2float(__ushort_as_half(pair.x)) * sc) ^ flip);
             }
         }
     }
@@ -282,9 +284,17 @@ __global__ void __launch_bounds__(256) comfy_transpose_kernel(const uint8_t* __r
             a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
             const uint32_t sc = e4m3_encode_soft(a / six_g);
             const float total = e4m3_to_float(sc) * g;
+            // four quotients by one divisor: the shared-reciprocal form returns the IEEE quotient for every quotient that can
+            // round to a non-zero code (common.cuh); totals outside its range take `/`
             float nq[4];
+            const SharedDivisor by_total = shared_divisor(total);
+            if (by_total.safe) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) nq[e] = total == 0.f ? 0.f : v[e] / total;
+                for (int e = 0; e < 4; ++e) nq[e] = by_total(v[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) nq[e] = total == 0.f ? 0.f : v[e] / total;
+            }
             const uint32_t two = e2m1_pair_hi_first(nq[0], nq[1]) | (e2m1_pair_hi_first(nq[2], nq[3]) << 8);
             const uint32_t next = __shfl_down_sync(0xffffffffu, two, 1);
             uint32_t packed_scales = sc;
